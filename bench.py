@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 gemm path on the LLM MLP block of the baseline's configs (q4 weights):
+
+    RMSNorm prologue -> gate/up GEMM  K=4096 -> 2 x 14336, SwiGLU epilogue -> down GEMM  K=14336 -> 4096, residual add
+
+One step = one pass of the block over M tokens (default 512): row statistics, the fused gate/up GEMM, the fused
+down GEMM.  `value` is TFLOP/s (2*M*N*K of both GEMMs over the device time of K steps, inputs resident in HBM);
+`e2e` is the same through the public API with HOST buffers (page-locked host -> device copy of the tokens and a
+device -> host read of the result inside the timed region).  Decode-sized M (1, 16) is measured next to it and
+reported as GB/s of the weight stream in `cases`.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m 512]
+
+With N > 1 (one process per GPU under torchrun) both weights are split column-wise (N) across the ranks; the
+SwiGLU output and the block output are all-gathered over NCCL.  The problem is fixed, so scaling is "strong".
+`--impl reference` times the reference's CPU path (the oracle port, all host threads) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HID, FF = 4096, 14336
+METRIC, UNIT = "q4 dequant-GEMM TFLOP/s (LLM MLP block: rms+gate/up swiglu, down resadd)", "TFLOP/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm": d["hbm_gbs"], "tensor": d["bf16_tflops"], "tensor_sustained": d.get("bf16_tflops_sustained"), "src": "measured"}
+    return {"hbm": 6650.0, "tensor": 1590.0, "tensor_sustained": 1400.0, "src": "fallback"}
+
+
+def block_flops(M):
+    return 2.0 * M * (2 * FF) * HID + 2.0 * M * HID * FF
+
+
+def block_bytes(M):
+    """algorithmic bytes of one block pass: weights once, fp32 tokens in, fp16 hidden out+in, fp32 residual read+write, stats, gamma"""
+    w = (2 * FF * HID + HID * FF) * 5 // 8
+    return w + M * HID * 4 + 2 * M * FF * 2 + 2 * M * HID * 4 + M * 8 + HID * 4
+
+
+def synth_q4(rows, cols, seed, P, tile_rows=2048):
+    """N(0, 0.02) weights quantised to q4g32a.t64.  A 2048-row slab is drawn and encoded, then repeated down the
+    tensor: records are independent 64 x 32 blocks, so the repeated bytes are a valid tensor with the same value
+    distribution (documented stand-in: the configs name no dataset)."""
+    rs = np.random.default_rng(seed)
+    tr = min(tile_rows, rows)
+    slab = P.packQ4((rs.standard_normal(tr * cols) * 0.02).astype(np.float32), tr, cols)
+    reps = -(-rows // tr)
+    return np.tile(slab, reps)[: rows * cols * 5 // 8]
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs"""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try: self.proc.wait(timeout=5)
+            except Exception: pass
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"): reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3):
+    """the reference's CPU path on a bounded sample of the block: M_rows tokens, the first gu_cols hidden columns of
+    the gate/up GEMM (RMS prologue, SwiGLU) and the first dn_cols output columns of the down GEMM (residual add)"""
+    import oracle as O
+    rs = np.random.default_rng(seed)
+    X = O.round_f16(rs.standard_normal(M_rows * HID).astype(np.float32))
+    gamma = (1 + 0.1 * rs.standard_normal(HID)).astype(np.float32)
+    Wgu, _ = O.pack_q4((rs.standard_normal(2 * gu_cols * HID) * 0.02).astype(np.float32), 2 * gu_cols, HID)
+    Wdn, _ = O.pack_q4((rs.standard_normal(dn_cols * FF) * 0.02).astype(np.float32), dn_cols, FF)
+    Hfull = O.to_f16(rs.standard_normal(M_rows * FF).astype(np.float32))
+    t0 = time.perf_counter()
+    ST = O.rowstats(X, M_rows, HID, rms=True)
+    Hh = np.zeros(M_rows * gu_cols, np.uint16)
+    O.gemm(enc="q4g32a.t64", X=X, W=Wgu, Y=Hh, M=M_rows, N=2 * gu_cols, K=HID, w_rows=2 * gu_cols, w_cols=HID, xmode="rms", epi="swiglu",
+           wr0=0, wr1=gu_cols, ldy=gu_cols, ST=ST, PV=gamma, threads=threads)
+    R = X[: M_rows * HID].reshape(M_rows, HID)[:, :dn_cols].copy()
+    O.gemm(enc="q4g32a.t64", X=Hfull, W=Wdn, Y=R, M=M_rows, N=dn_cols, K=FF, w_rows=dn_cols, w_cols=FF, epi="resadd", threads=threads)
+    dt = time.perf_counter() - t0
+    fl = 2.0 * M_rows * (2 * gu_cols) * HID + 2.0 * M_rows * dn_cols * FF
+    return fl, dt
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's own CPU implementation of the path (oracle port; the reference is JavaScript
+    and no JavaScript engine exists here), all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    import oracle as O
+    O.build()
+    thr = O.max_threads()
+    rows, gu, dn = 64, 1024, 512
+    for _ in range(args.warmup): cpu_sample(1, 256, 128, thr)
+    t = 0.0; fl = 0.0
+    for _ in range(args.steps):
+        f, d = cpu_sample(rows, gu, dn, thr); fl += f; t += d
+    v = fl / t / 1e12
+    sample = f"{rows} tokens x {gu} of {FF} hidden columns (gate/up, rms+swiglu) + {dn} of {HID} output columns (down, resadd), float64 accumulate"
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": t / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate of f16 products",
+                      "data": "synthetic", "config": {"workload": f"LLM MLP block q4, M={args.m} (configs[1]); CPU sample per step: {sample}"},
+                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": thr, "kind": "port", "sample": sample},
+                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=512, help="tokens per step of the headline (512 = the tensor-bound case of the config)")
+    ap.add_argument("--copies", type=int, default=3, help="weight copies rotated through so that every step streams from HBM")
+    ap.add_argument("--skip-cases", action="store_true", help="only the headline (for profiler captures)")
+    ap.add_argument("--kernel", default=None, help="force a kernel family (generic | decode | umma)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import torch
+    import torch.distributed as dist
+    import p0pc0rn_kernels_b200 as P
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    gpu = P.createGpu({"device": local, "stream": torch.cuda.current_stream().cuda_stream})
+    pk = peaks()
+
+    # ---- model state: this rank's column shard of both weights (the whole weights at N = 1), `copies` times
+    ffl, hidl = FF // world, HID // world
+    gu_full = synth_q4(2 * FF, HID, 1, P); dn_full = synth_q4(HID, FF, 2, P)
+    gu_mine = P.shard_swiglu_bytes(gu_full, "q4g32a.t64", FF, HID, rank, world)
+    dn_mine = P.shard_bytes(dn_full, "q4g32a.t64", HID, FF, rank, world)
+    del gu_full, dn_full
+    Wgu = [gpu.upload(gu_mine, f"gate_up.{i}") for i in range(args.copies)]
+    Wdn = [gpu.upload(dn_mine, f"down.{i}") for i in range(args.copies)]
+    gamma = gpu.upload((1 + 0.1 * np.random.default_rng(4).standard_normal(HID)).astype(np.float32), "gamma")
+    w_bytes = gu_mine.nbytes + dn_mine.nbytes
+    Mmax = max(args.m, 16)
+
+    def wrap(t):
+        return gpu.wrap(t.data_ptr(), t.numel() * t.element_size())
+
+    st_t = torch.zeros(Mmax * 2, dtype=torch.float32, device=dev); st = wrap(st_t)
+    x_t = torch.zeros(Mmax * HID, dtype=torch.float32, device=dev); xb = wrap(x_t)                  # residual stream in (fp32)
+    hl_t = torch.zeros(Mmax * ffl, dtype=torch.float16, device=dev); hl = wrap(hl_t)                # this rank's SwiGLU columns
+    hf_t = hl_t if world == 1 else torch.zeros(Mmax * FF, dtype=torch.float16, device=dev)          # the full hidden row
+    hf = hl if world == 1 else wrap(hf_t)
+    x_host = np.random.default_rng(5).standard_normal(Mmax * HID).astype(np.float32)
+    x_t.copy_(torch.from_numpy(x_host))
+    launches = {"n": 0}
+
+    def block(M, i, gather=True):
+        """one pass of the MLP block over M tokens with weight copy i"""
+        P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
+        a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
+             "y": {"buf": hl, "ld": ffl}, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
+        if args.kernel: a["kernel"] = args.kernel
+        P.gemm(gpu, a)
+        if world > 1 and gather:
+            hf_t[: M * FF].view(M, FF).copy_(P.all_gather_columns(hl_t[: M * ffl].view(M, ffl)))
+        # residual add, in place, into this rank's columns of the (replicated) fp32 residual stream
+        a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
+             "y": {"buf": xb, "ld": HID, "n0": rank * hidl}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
+        if args.kernel: a["kernel"] = args.kernel
+        P.gemm(gpu, a)
+        if world > 1 and gather:
+            xv = x_t[: M * HID].view(M, HID)
+            xv.copy_(P.all_gather_columns(xv[:, rank * hidl:(rank + 1) * hidl]))
+
+    def timed(M, steps, warmup, gather=True):
+        for s in range(warmup): block(M, s % args.copies, gather)
+        torch.cuda.synchronize()
+        if world > 1: dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = gpu.launches
+        e0.record()
+        for s in range(steps): block(M, s % args.copies, gather)
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1: dist.barrier()
+        ms = e0.elapsed_time(e1)
+        launches["n"] = gpu.launches - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        return ms / steps
+
+    def kernel_ms(M, which, reps):
+        """average device time of ONE kernel of the block (gate/up or down), CUDA events around each launch"""
+        evs = []
+        for s in range(reps + 2):
+            i = s % args.copies
+            P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
+            if which == "gate_up":
+                a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
+                     "y": {"buf": hl, "ld": ffl}, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
+            else:
+                a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
+                     "y": {"buf": xb, "ld": HID, "n0": rank * hidl}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
+            if args.kernel: a["kernel"] = args.kernel
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); P.gemm(gpu, a); e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return float(np.mean([a.elapsed_time(b) for a, b in evs[2:]])), gpu.lastKernel
+
+    # ---- headline: K timed steps at M = args.m
+    M = args.m
+    sampler = ClockSampler(local);
+    if rank == 0: sampler.start()
+    ms = timed(M, args.steps, max(3, args.warmup))
+    n_launch = launches["n"]
+    gu_ms, gu_kernel = kernel_ms(M, "gate_up", min(20, args.steps))
+    clocks = sampler.stop() if rank == 0 else None
+    value = block_flops(M) / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers: upload tokens, run, read the result
+    import ctypes as C
+    from p0pc0rn_kernels_b200._lib import lib
+    hp = C.c_void_p(); gpu._check(lib.p0p_host_alloc(gpu._h, M * HID * 4, C.byref(hp)))
+    pin_in = np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_float)), shape=(M * HID,)); pin_in[:] = x_host[: M * HID]
+    out_bytes = M * HID * 4
+
+    def e2e_step(i):
+        gpu.upload(pin_in, "", xb, 0)           # the step's tokens (fp32 residual stream), page-locked host -> device
+        block(M, i)
+        return gpu.read(xb, 0, out_bytes)       # the updated residual stream, device -> host
+
+    for s in range(3): e2e_step(s % args.copies)
+    torch.cuda.synchronize()
+    if world > 1: dist.barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(5, min(args.steps, 30))
+    for s in range(n_e2e): e2e_step(s % args.copies)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_ms = float(t.item())
+    h2d = M * HID * 4
+    e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms}
+
+    # ---- decode-sized cases of the same config (HBM-bound): GB/s of the algorithmic bytes
+    cases = []
+    if not args.skip_cases:
+        for Mc in (1, 16):
+            msc = timed(Mc, max(20, args.steps), 5, gather=True)
+            gbs = block_bytes(Mc) / world / (msc * 1e-3) / 1e9 if world > 1 else block_bytes(Mc) / (msc * 1e-3) / 1e9
+            kms, kk = kernel_ms(Mc, "gate_up", 20)
+            kb = (2 * ffl * HID * 5 // 8) + Mc * HID * 4 + Mc * ffl * 2
+            cases.append({"M": Mc, "ms_per_step": msc, "GB/s": gbs * (world if world > 1 else 1), "TFLOP/s": block_flops(Mc) / (msc * 1e-3) / 1e12,
+                          "gate_up_kernel": {"ms": kms, "GB/s": kb / (kms * 1e-3) / 1e9, "frac_hbm": kb / (kms * 1e-3) / 1e9 / pk["hbm"], "family": P._lib.KERNEL_NAMES.get(kk)}})
+
+    # ---- roofline of the dominant kernel (gate/up GEMM: 2/3 of the block's FLOPs)
+    gu_flops = 2.0 * M * (2 * ffl) * HID
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tp):
+        traffic = json.load(open(tp)).get(f"gate_up_M{M}_{P._lib.KERNEL_NAMES.get(gu_kernel)}")
+    roof = {"bound": "tensor", "achieved": gu_flops / (gu_ms * 1e-3) / 1e12, "peak": pk["tensor"], "unit": "TFLOP/s", "traffic": traffic,
+            "kernel": f"gate/up GEMM ({P._lib.KERNEL_NAMES.get(gu_kernel)} family), M={M}", "ms_per_launch": gu_ms, "peak_source": pk["src"] + " (burst cuBLAS bf16)"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+
+    if rank == 0:
+        # CPU baseline: the oracle port on a bounded sample, all host threads
+        import oracle as O
+        O.build(); thr = O.max_threads()
+        cpu_sample(1, 256, 128, thr)
+        f, d = cpu_sample(64, 1024, 512, thr)
+        cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port",
+               "sample": f"64 tokens x 1024 of {FF} hidden columns (gate/up) + 512 of {HID} output columns (down), float64 accumulate, {d:.1f} s"}
+        out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (q4 weights dequantised in-kernel)",
+               "data": "synthetic",
+               "config": {"workload": f"LLM MLP block q4, M={M} tokens: rowstats + gate/up K4096->2x14336 (rms, swiglu) + down K14336->4096 (resadd) (configs[1])",
+                          "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + (" + NCCL all-gather of hidden and output" if world > 1 else ""),
+                          "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)"},
+               "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
+               "GB/s": block_bytes(M) / (ms * 1e-3) / 1e9}
+        print(json.dumps(out))
+    lib.p0p_host_free(gpu._h, hp)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+    gpu.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,309 @@
+"""Parity of the CUDA gemm path with the CPU oracle, through the public API (C ABI underneath).
+
+The first block restates the reference's own GEMM-family tests one for one (test/kernels.test.js:72-145,
+198-221): same shapes, seeds, generators and pass criterion, plus the tighter gates of tests/cases.py.  The
+second block covers what the reference's tests leave out: every fused prologue and epilogue and the sub-range
+arguments, against the oracle's restatement of the shader arithmetic (src/ops/gemm.js:60-101, 191-254)."""
+import numpy as np
+import pytest
+
+import cases as CS
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = [None, "generic"]   # None = the library's own choice
+
+
+def P():
+    import p0pc0rn_kernels_b200 as P_
+    return P_
+
+
+# ------------------------------------------------------------------------------------------------ reference cases
+@pytest.mark.parametrize("acc", ["f32", "f16"])
+@pytest.mark.parametrize("enc", ["f16", "q4g32a.t64", "q8g64s.t64"])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_ref_gemm_encodings(gpu, oracle, enc, acc, kernel):
+    """GEMM, three weight encodings x two accumulate modes: M32 N128 K256, seeds 7 / 11 (0.05) (test/kernels.test.js:72-84)"""
+    O = oracle
+    M, N, K = 32, 128, 256
+    X = O.round_f16(O.randn(M * K, 7)); W0 = O.randn(N * K, 11, 0.05)
+    Wb, Wd = CS.encode(enc, W0, N, K)
+    wb, xb, yb = gpu.upload(Wb), gpu.upload(P().toF16(X)), gpu.buffer(M * N * 2)
+    try:
+        a = {"w": {"enc": enc, "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": {"buf": xb}, "y": {"buf": yb}, "M": M, "N": N, "K": K, "acc": acc}
+        if kernel: a["kernel"] = kernel
+        P().gemm(gpu, a)
+        got = P().fromF16(gpu.read(yb, 0, M * N * 2).view(np.uint16))
+        want = O.cpu_gemm(X, Wd, M, N, K)
+        cos, _ = O.compare(got, want)
+        assert cos > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), f"gemm {enc}")
+    finally:
+        for b in (wb, xb, yb): gpu.free(b)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_ref_partial_tiles(gpu, oracle, kernel):
+    """GEMM, partial tiles M33 N192 K256 f16, seeds 17 / 19 (test/kernels.test.js:85-92)"""
+    O = oracle
+    M, N, K = 33, 192, 256
+    X = O.round_f16(O.randn(M * K, 17)); Wd = O.round_f16(O.randn(N * K, 19, 0.05))
+    wb, xb, yb = gpu.upload(P().toF16(Wd)), gpu.upload(P().toF16(X)), gpu.buffer(M * N * 2)
+    try:
+        a = {"w": {"enc": "f16", "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": {"buf": xb}, "y": {"buf": yb}, "M": M, "N": N, "K": K}
+        if kernel: a["kernel"] = kernel
+        P().gemm(gpu, a)
+        got = P().fromF16(gpu.read(yb, 0, M * N * 2).view(np.uint16))
+        want = O.cpu_gemm(X, Wd, M, N, K)
+        assert O.compare(got, want)[0] > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), "partial tiles")
+    finally:
+        for b in (wb, xb, yb): gpu.free(b)
+
+
+C3 = {"T": 5, "H": 6, "W": 6, "C": 32, "N": 128}   # test/kernels.test.js:95
+
+
+def conv3_setup(gpu, O, seed_x=31, seed_w=33):
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    X = O.round_f16(O.randn(T * H * W * C, seed_x)); Wt = O.round_f16(O.randn(N * 27 * C, seed_w, 0.03))
+    return {"X": X, "Wt": Wt, "xb": gpu.upload(P().toF16(X)), "wb": gpu.upload(P().toF16(Wt))}
+
+
+def conv3(gpu, s, x, y, t0, nf, padL=0, ks=1, tile=None, kernel=None):
+    """output frames [t0, t0 + nf) of the clip (test/kernels.test.js:101-105)"""
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    a = {"w": {"enc": "f16", "buf": s["wb"], "off": 0, "bytes": s["wb"]._pf, "rows": N, "cols": 27 * C}, "x": x, "y": y, "M": nf * H * W, "N": N, "K": 27 * C,
+         "conv": {"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": t0, "padL": padL, "ks": ks}}
+    if tile: a["tile"] = tile
+    if kernel: a["kernel"] = kernel
+    P().gemm(gpu, a)
+
+
+@pytest.mark.parametrize("tile", [None, {"BM": 128, "BN": 128}, {"BM": 64, "BN": 64}, {"BM": 32, "BN": 128}, {"BM": 128, "BN": 64}])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_ref_conv3(gpu, oracle, tile, kernel):
+    """3x3x3 convolution over a THWC clip, and at the tiles the tuning table can pick (test/kernels.test.js:106-122)"""
+    O = oracle
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    s = conv3_setup(gpu, O); yb = gpu.buffer(T * H * W * N * 2)
+    try:
+        conv3(gpu, s, {"buf": s["xb"]}, {"buf": yb}, 0, T, tile=tile, kernel=kernel)
+        got = P().fromF16(gpu.read(yb, 0, T * H * W * N * 2).view(np.uint16))
+        want = O.cpu_conv3(s["X"], s["Wt"], T, H, W, C, N)
+        assert O.compare(got, want)[0] > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), "conv3")
+    finally:
+        for b in (s["xb"], s["wb"], yb): gpu.free(b)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_ref_conv3_chunks_bit_identical(gpu, oracle, kernel):
+    """conv3 in time chunks of 2 frames = the whole clip, bit for bit (test/kernels.test.js:123-131)"""
+    O = oracle
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    s = conv3_setup(gpu, O); n = T * H * W * N
+    ya, yb = gpu.buffer(n * 2), gpu.buffer(n * 2); fx, fy = H * W * C * 2, H * W * N * 2
+    try:
+        conv3(gpu, s, {"buf": s["xb"]}, {"buf": ya}, 0, T, kernel=kernel)
+        for t0 in range(0, T, 2):
+            padL = max(0, t0 - 1)
+            conv3(gpu, s, {"buf": s["xb"], "off": padL * fx}, {"buf": yb, "off": t0 * fy}, t0, min(2, T - t0), padL, kernel=kernel)
+        a, b = gpu.read(ya, 0, n * 2).view(np.uint16), gpu.read(yb, 0, n * 2).view(np.uint16)
+        assert np.array_equal(a, b), "chunked conv3 DIFFERS from the whole clip"
+    finally:
+        for x in (s["xb"], s["wb"], ya, yb): gpu.free(x)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_ref_conv3_ring_bit_identical(gpu, oracle, kernel):
+    """conv3 from a ring of 3 frames = the whole clip, bit for bit (test/kernels.test.js:132-145)"""
+    O = oracle
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    s = conv3_setup(gpu, O); n = T * H * W * N
+    ya, yb = gpu.buffer(n * 2), gpu.buffer(n * 2); fx, fy = H * W * C, H * W * N * 2
+    ring = gpu.buffer(3 * fx * 2); X16 = P().toF16(s["X"])
+    try:
+        conv3(gpu, s, {"buf": s["xb"]}, {"buf": ya}, 0, T, kernel=kernel)
+        for t in range(T):
+            for g in sorted({max(0, t - 1), t, min(T - 1, t + 1)}):
+                gpu.device.queue.writeBuffer(ring, (g % 3) * fx * 2, X16, g * fx, fx)
+            conv3(gpu, s, {"buf": ring}, {"buf": yb, "off": t * fy}, t, 1, 0, 3, kernel=kernel)
+            gpu.done()   # the ring is rewritten for the next frame
+        a, b = gpu.read(ya, 0, n * 2).view(np.uint16), gpu.read(yb, 0, n * 2).view(np.uint16)
+        assert np.array_equal(a, b), "ring conv3 DIFFERS from the whole clip"
+    finally:
+        for x in (s["xb"], s["wb"], ya, yb, ring): gpu.free(x)
+
+
+def test_ref_converted_bf16_linear_q4(gpu, oracle):
+    """a BF16 linear layer, converted to 4-bit, through the GEMM (test/kernels.test.js:198-209)"""
+    O = oracle
+    M, N, K = 32, 192, 512
+    Wb16 = O.to_bf16(O.randn(N * K, 81, 0.05)); X = O.round_f16(O.randn(M * K, 83))
+    file = P().writeSafetensors({"layers.0.mlp.up_proj.weight": {"dtype": "BF16", "shape": [N, K], "data": Wb16.view(np.uint8)}})
+    r = P().convertSafetensors(file, {"bits": 4}); model = P().uploadWeights(gpu, r["manifest"], r["shards"])
+    w = model.tensor("layers.0.mlp.up_proj.weight")
+    _, deq = O.pack_q4(O.from_bf16(Wb16), N, K)
+    xb, yb = gpu.upload(P().toF16(X)), gpu.buffer(M * N * 2)
+    try:
+        assert w["enc"] == "q4g32a.t64"
+        P().gemm(gpu, {"w": w, "x": {"buf": xb}, "y": {"buf": yb}, "M": M, "N": N, "K": K})
+        got = P().fromF16(gpu.read(yb, 0, M * N * 2).view(np.uint16)); want = O.cpu_gemm(X, deq, M, N, K)
+        assert O.compare(got, want)[0] > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), "converted q4")
+    finally:
+        model.free(); gpu.free(xb); gpu.free(yb)
+
+
+def test_ref_converted_conv3_weight(gpu, oracle):
+    """a 3x3x3 conv weight in PyTorch layout [O, I, kt, kh, kw] through the 3D convolution (test/kernels.test.js:210-221)"""
+    O = oracle
+    T, H, W, C, N = (C3[k] for k in "THWCN")
+    src = O.round_f16(O.randn(N * C * 27, 87, 0.03)); X = O.round_f16(O.randn(T * H * W * C, 89))
+    file = P().writeSafetensors({"decoder.conv.weight": {"dtype": "F16", "shape": [N, C, 3, 3, 3], "data": P().toF16(src).view(np.uint8)}})
+    r = P().convertSafetensors(file, {"bits": 16}); model = P().uploadWeights(gpu, r["manifest"], r["shards"]); w = model.tensor("decoder.conv.weight")
+    ref = src.reshape(N, C, 27).transpose(0, 2, 1).reshape(-1).copy()   # ref[n][tap][c] = src[n][c][tap]
+    xb, yb = gpu.upload(P().toF16(X)), gpu.buffer(T * H * W * N * 2)
+    try:
+        P().gemm(gpu, {"w": w, "x": {"buf": xb}, "y": {"buf": yb}, "M": T * H * W, "N": N, "K": 27 * C,
+                       "conv": {"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": 0, "padL": 0, "ks": 1}})
+        got = P().fromF16(gpu.read(yb, 0, T * H * W * N * 2).view(np.uint16)); want = O.cpu_conv3(X, ref, T, H, W, C, N)
+        assert O.compare(got, want)[0] > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), "converted conv3")
+    finally:
+        model.free(); gpu.free(xb); gpu.free(yb)
+
+
+def test_readme_quick_start(gpu):
+    """README.md:52-63: 0.5 x 0.01 over K = 512 is about 2.56 everywhere"""
+    M, N, K = 64, 256, 512
+    x = gpu.upload(P().toF16(np.full(M * K, 0.5, np.float32))); w = gpu.upload(P().toF16(np.full(N * K, 0.01, np.float32))); y = gpu.buffer(M * N * 2)
+    try:
+        P().gemm(gpu, {"w": {"enc": "f16", "buf": w, "off": 0, "bytes": N * K * 2, "rows": N, "cols": K}, "x": {"buf": x}, "y": {"buf": y}, "M": M, "N": N, "K": K})
+        out = P().fromF16(gpu.read(y, 0, M * N * 2).view(np.uint16))
+        assert np.allclose(out, 2.56, atol=5e-3)
+    finally:
+        for b in (x, w, y): gpu.free(b)
+
+
+# ------------------------------------------------------------------------------------------------ beyond the reference's tests
+HEADS = {"Ltot": 80, "Hq": 2, "Hkv": 1, "rowOff": 8, "eps": 1e-6}
+EXTRA = [
+    dict(name="f32 store", enc="q4", M=40, N=128, K=256, epi="f32"),
+    dict(name="resadd plain", enc="q4", M=40, N=192, K=256, epi="resadd"),
+    dict(name="resadd gate+bias", enc="q8", M=40, N=192, K=256, epi="resadd", gate=True, bias=True, ev_off=8, bv_off=4),
+    dict(name="resadd store", enc="f16", M=40, N=128, K=256, epi="resadd", gate=True, store=True),
+    dict(name="swiglu", enc="q4", M=40, N=256, K=256, epi="swiglu"),
+    dict(name="swiglu bias rows", enc="q4", M=40, N=256, K=256, epi="swiglu", bias=True, wr0=64, wr1=256, w_rows=448),
+    dict(name="geglu", enc="q8", M=24, N=256, K=256, epi="swiglu", act="gelu"),
+    dict(name="bias", enc="f16", M=40, N=128, K=256, epi="bias", ev_off=16),
+    dict(name="bias+res", enc="q4", M=40, N=128, K=256, epi="bias", res=True),
+    dict(name="heads interleaved", enc="q8", M=40, N=512, K=256, epi="heads", heads=dict(HEADS)),
+    dict(name="heads half", enc="q4", M=40, N=512, K=256, epi="heads", heads=dict(HEADS, ropeMode="half")),
+    dict(name="onormgate", enc="q4", M=24, N=256, K=256, epi="onormgate", Ltot=256),
+    dict(name="rms", enc="q4", M=40, N=128, K=256, xmode="rms", st_off=3, pv_off=8),
+    dict(name="lnmod", enc="q8", M=40, N=128, K=256, xmode="lnmod", x_shift=0.7),
+    dict(name="rms+swiglu", enc="q4", M=40, N=256, K=512, xmode="rms", epi="swiglu"),
+    dict(name="lnmod+heads", enc="q8", M=40, N=384, K=256, xmode="lnmod", epi="heads", heads=dict(Ltot=40, Hq=1, Hkv=1, rowOff=0, eps=1e-6)),
+    dict(name="sub-ranges", enc="q4", M=20, N=128, K=128, ldx=320, kx0=64, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="sub-ranges f16 ld", enc="f16", M=20, N=128, K=128, ldx=320, kx0=64, wk0=128, w_cols=256, w_ld=264, wr0=3, w_rows=140, ldy=200, ny0=40),
+    dict(name="byte offsets", enc="q8", M=20, N=128, K=128, x_off=256, w_off=512, y_off=768),
+    dict(name="M=1", enc="q4", M=1, N=256, K=512),
+    dict(name="M=16 q8", enc="q8", M=16, N=256, K=512),
+    dict(name="tail columns", enc="f16", M=17, N=100, K=96, w_rows=100),
+]
+CONV = [
+    dict(name="conv3x3", enc="f16", M=8 * 8, N=64, K=9 * 32, x_elems=8 * 8 * 32, w_scale=0.03,
+         conv=dict(kind="conv", Hi=8, Wi=8, Ci=32, Ho=8, Wo=8, stride=1, padT=1, padL=1, ks=3)),
+    dict(name="conv3x3 stride2", enc="f16", M=4 * 4, N=64, K=9 * 32, x_elems=8 * 8 * 32, w_scale=0.03,
+         conv=dict(kind="conv", Hi=8, Wi=8, Ci=32, Ho=4, Wo=4, stride=2, padT=1, padL=1, ks=3)),
+    dict(name="conv1x1", enc="q4", M=8 * 8, N=64, K=64, x_elems=8 * 8 * 64, conv=dict(kind="conv", Hi=8, Wi=8, Ci=64, Ho=8, Wo=8, stride=1, padT=0, padL=0, ks=1)),
+    dict(name="conv up2+gn", enc="f16", M=16 * 16, N=64, K=9 * 32, x_elems=8 * 8 * 32, w_scale=0.03, epi="bias",
+         conv=dict(kind="conv", Hi=8, Wi=8, Ci=32, Ho=16, Wo=16, stride=1, padT=1, padL=1, ks=3, up2=True, gn=True)),
+    dict(name="conv3 pn", enc="f16", M=3 * 5 * 6, N=64, K=27 * 32, x_elems=3 * 5 * 6 * 32, w_scale=0.03, epi="bias",
+         conv=dict(kind="conv3", Hi=5, Wi=6, Ci=32, Ho=5, Wo=6, stride=3, padT=0, padL=0, ks=1, pn=True)),
+]
+
+
+@pytest.mark.parametrize("case", EXTRA + CONV, ids=lambda c: c["name"])
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_fused_variants(gpu, oracle, case, kernel):
+    h = CS.build(dict(case, kernel=kernel))
+    got = CS.run_gpu(gpu, h)
+    want = CS.run_oracle(h)
+    CS.check(got, want, case["name"])
+
+
+@pytest.mark.parametrize("enc,scale", [("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q4g32a.t64", "offset"), ("f16", 0.05)])
+@pytest.mark.parametrize("path", [0, 1])
+def test_dequant_bit_exact(gpu, oracle, enc, scale, path):
+    """every tile value the kernels multiply with equals f16(deq) of the encoder, bit for bit (docs/FORMAT.md)"""
+    import ctypes as C
+    from p0pc0rn_kernels_b200._lib import ENC, lib
+    O = oracle
+    N, K = 192, 256
+    if scale == "offset":   # groups that sit far from zero: min >> scale, where a single fp16 fma could double-round
+        W0 = (1.0 + 1e-4 * O.randn(N * K, 3)).astype(np.float32) * np.repeat(np.float32(10.0) ** np.random.default_rng(1).integers(-3, 3, N * K // 32), 32).astype(np.float32)
+    else:
+        W0 = O.randn(N * K, 11, scale)
+    Wb, deq = CS.encode(enc, W0, N, K)
+    wb, ob = gpu.upload(Wb), gpu.buffer(N * K * 2)
+    try:
+        gpu._check(lib.p0p_dequant(gpu._h, ENC[enc], wb.handle, 0, K, 0, 0, N, path, ob.handle, 0))
+        got = gpu.read(ob, 0, N * K * 2).view(np.uint16)
+        assert np.array_equal(got, O.to_f16(deq)), f"{int((got != O.to_f16(deq)).sum())} of {N * K} tile values differ"
+    finally:
+        gpu.free(wb); gpu.free(ob)
+
+
+def test_rowstats(gpu, oracle):
+    O = oracle
+    rows, cols = 37, 1000
+    X = (O.randn(rows * cols, 5) + 0.3).astype(np.float32)
+    xb, sb = gpu.upload(X), gpu.buffer((rows + 2) * 8)
+    try:
+        for mode in ("ln", "rms"):
+            P().rowstats(gpu, {"x": {"buf": xb}, "rows": rows, "cols": cols, "mode": mode, "eps": 1e-6, "st": {"buf": sb, "off": 2}})
+            got = gpu.read(sb, 16, rows * 8).view(np.float32)
+            want = O.rowstats(X, rows, cols, rms=(mode == "rms"))
+            assert np.allclose(got, want, rtol=2e-5, atol=1e-6)
+    finally:
+        gpu.free(xb); gpu.free(sb)
+
+
+def test_errors(gpu):
+    """bad arguments raise with the reference's messages (src/ops/gemm.js:271, 283, 313); the context stays usable"""
+    b = gpu.buffer(4096)
+    try:
+        with pytest.raises(ValueError, match="unsupported weight encoding"):
+            P().gemm(gpu, {"w": {"enc": "q2", "buf": b, "rows": 64, "cols": 32}, "x": {"buf": b}, "y": {"buf": b}, "M": 1, "N": 64, "K": 32})
+        with pytest.raises(ValueError, match="K must be a multiple of 32"):
+            P().gemm(gpu, {"w": {"enc": "f16", "buf": b, "rows": 8, "cols": 48}, "x": {"buf": b}, "y": {"buf": b}, "M": 1, "N": 8, "K": 48})
+        with pytest.raises(ValueError, match="missing binding"):
+            P().gemm(gpu, {"w": {"enc": "f16", "buf": b, "rows": 8, "cols": 32}, "x": {"buf": b, "mode": "rms"}, "y": {"buf": b}, "M": 1, "N": 8, "K": 32})
+        with pytest.raises(ValueError, match="bytes"):
+            P().gemm(gpu, {"w": {"enc": "f16", "buf": b, "rows": 64, "cols": 64}, "x": {"buf": b}, "y": {"buf": b}, "M": 64, "N": 64, "K": 64, "epi": "f32"})
+        with pytest.raises(ValueError, match="bad tile"):
+            P().gemm(gpu, {"w": {"enc": "f16", "buf": b, "rows": 8, "cols": 32}, "x": {"buf": b}, "y": {"buf": b}, "M": 1, "N": 8, "K": 32, "tile": {"BM": 48, "BN": 64}})
+        gpu.done()
+        assert not gpu.lost
+    finally:
+        gpu.free(b)
+
+
+def test_buffers(gpu):
+    """zero-filled buffers, 16-byte rounding, same-size pool reuse, double free (src/core/gpu.js:87-139)"""
+    a = gpu.buffer(100)
+    assert a._pf == 112 and not gpu.read(a).any()
+    gpu.upload(np.full(100, 7, np.uint8), "", a, 4)
+    assert gpu.read(a, 4, 100).tolist() == [7] * 100
+    s0 = gpu.poolStats()
+    gpu.free(a); gpu.free(a)
+    b = gpu.buffer(100)
+    assert not gpu.read(b).any(), "a pooled buffer must come back cleared"
+    assert gpu.poolStats()["reuses"] >= s0["reuses"]
+    gpu.free(b)
+    with pytest.raises(ValueError):
+        gpu.read(b.__class__(gpu, b.handle, 16), 0, 16)
