@@ -165,7 +165,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    gpu = P.createGpu({"device": local, "stream": torch.cuda.current_stream().cuda_stream})
+    # every launch of the library and every torch op / event below shares ONE non-default stream
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    gpu = P.createGpu({"device": local, "stream": stream.cuda_stream})
     pk = peaks()
 
     # ---- model state: this rank's column shard of both weights (the whole weights at N = 1), `copies` times

@@ -45,11 +45,14 @@ enum {                                                                       /* 
 /* which kernel family served the last p0p_gemm call (p0p_last_kernel) or is forced (p0p_gemm_args.force_kernel) */
 enum { P0P_K_AUTO = 0, P0P_K_GENERIC = 1, P0P_K_DECODE = 2, P0P_K_UMMA = 3 };
 
+enum { P0P_OPT_USE_STREAM = 1 };
+
 /* ---- context ------------------------------------------------------------------------------------------- */
 typedef struct p0p_opts {
   uint32_t struct_size;        /* sizeof(p0p_opts) */
-  uint32_t flags;              /* reserved, 0 */
-  void*    stream;             /* an existing cudaStream_t to enqueue on, or NULL for a stream the context owns */
+  uint32_t flags;              /* P0P_OPT_* */
+  void*    stream;             /* with P0P_OPT_USE_STREAM: the cudaStream_t to enqueue on (NULL = the legacy default stream);
+                                  otherwise ignored and the context creates and owns a stream */
 } p0p_opts;
 
 /* createGpu(opts) (src/core/gpu.js:15-20, 41-77): open device `device` (ordinal). */

@@ -37,6 +37,9 @@ struct p0p_ctx {
   void* scratch = nullptr;
   uint64_t scratch_bytes = 0;
   std::unordered_set<void*> pinned;
+  // a host-visible word kernels write when a bounded wait runs out (0 = fine)
+  int* host_status = nullptr;
+  int* dev_status = nullptr;
 };
 
 namespace p0p {

@@ -40,6 +40,7 @@ extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a, double* flops) {
   if ((uint64_t)a->wk0 + K > a->w_cols) return fail(c, -5, "gemm: wk0 + K exceeds the weight's %u columns", a->w_cols);
   if (a->enc != P0P_ENC_F16 && (a->wk0 % 32u)) return fail(c, -5, "gemm: wk0 must be a multiple of 32 for quantised weights");
   if (!a->w_rows) return fail(c, -5, "gemm: the weight has no rows");
+  if (a->wr0 >= a->w_rows) return fail(c, -5, "gemm: wr0 %u is past the weight's %u rows", a->wr0, a->w_rows);
 
   KP p{};
   p.M = M; p.N = N; p.K = K; p.ldx = a->ldx ? a->ldx : K; p.kx0 = a->kx0; p.wR0 = a->wr0; p.wR1 = a->wr1;

@@ -1,7 +1,364 @@
+// Decode-sized multiply (M <= 16 tokens, q4 / q8 weights): the call is bound by streaming the weights out of
+// HBM once, so the kernel is built around that stream.
+//
+//   stage 1  k_decode_stream   The (64-row tile) x (k-block) units of the weight are spread evenly over a grid of
+//            about three blocks per SM.  In each block one producer lane moves whole records from global to
+//            shared memory with bulk asynchronous copies (cp.async.bulk, mbarrier-tracked, a ring of stages);
+//            four consumer warps each own 16 rows of the tile.  Codes go to the tensor cores WITHOUT being
+//            dequantised: a 4-bit code q becomes the fp16 bit pattern 0x6400|q (= 1024+q) or 0x6400|q<<4
+//            (= 1024+16q) by one lop3, an 8-bit code the pattern 0x6400|(q+128), and mma.sync.m16n8k16
+//            (weights = A, tokens = B, fp32 accumulate) sums code*x over one group.  The group's scale and
+//            minimum are applied to the fp32 sum afterwards:  y += s * (acc - C) + mn * Sx,  where
+//            C (the sum of the pattern offsets times x) and Sx (the sum of x) depend only on the tokens and
+//            are tabulated once per k-block.  The tokens are staged in shared memory in the operand order
+//            of the instruction, with the fused prologue (plain fp16 / RMSNorm / LayerNorm+modulation)
+//            applied on the way in.  Each unit's 64 x M partial sums go to a scratch buffer.
+//   stage 2  k_decode_finish   sums the k-block partials in a fixed order (deterministic, no atomics) and
+//            applies the fused epilogue.
+//
+// Every wait on an mbarrier is bounded; on a time-out the block records a code in the context's status word
+// and leaves.
 #pragma once
 #include "common.cuh"
 #include "ctx.h"
+#include "epilogue.cuh"
+#include "sync.cuh"
+
 namespace p0p {
-inline bool decode_supported(const KP&) { return false; }
-inline int launch_decode(p0p_ctx*, const KP&) { return -9; }
+
+constexpr int D_CONSUMERS = 128;            // 4 warps x 16 rows
+constexpr int D_THREADS = D_CONSUMERS + 32; // + the producer warp
+constexpr int D_STAGES = 6;
+constexpr int D_STAGE_K = 128;              // k per stage: 4 q4 records (5120 B) or 2 q8 records (8448 B)
+constexpr int D_STAGE_BYTES = 8448;
+constexpr int D_MAX_KC = 4096;              // largest k-block
+
+struct DecodeP {
+  KP p;
+  uint32_t Mp;        // token columns fed to the tensor core: 8 or 16
+  uint32_t tiles;     // 64-row tiles the call touches (swiglu: gate tiles then up tiles)
+  uint32_t th;        // swiglu: tiles per half; else = tiles
+  uint32_t KC, S;     // k-block length (multiple of 128) and count
+  uint32_t units;     // tiles * S
+  uint32_t nslots;    // tiles * 64
+  float* scratch;     // [S][M][nslots] fp32
+  int* status;
+};
+
+// weight tile index (64 rows) of unit-local tile t
+__device__ __forceinline__ uint32_t d_tile_row0(const DecodeP& d, uint32_t t) {
+  if (d.p.epi == P0P_EPI_SWIGLU) return t < d.th ? d.p.wR0 + t * 64u : d.p.wR1 + (t - d.th) * 64u;
+  return d.p.wR0 + t * 64u;
 }
+
+// ---- token staging: one thread per (token, 32-k group).  Writes the group's 64 bytes in operand order and
+// its (C, Sx) pair.
+template <int ENC, int XMODE>
+__device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float2* cs, uint32_t tok_stride, uint32_t tid) {
+  const KP& p = d.p;
+  const uint32_t groups = klen / 32u;
+  for (uint32_t it = tid; it < p.M * groups; it += D_CONSUMERS) {
+    const uint32_t m = it / groups, gi = it % groups, k0 = kb0 + gi * 32u;
+    float v[32];
+    if (XMODE == P0P_X_F16) {
+      const __half* src = reinterpret_cast<const __half*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
+      if (p.vecx) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); v[q * 8 + 2 * i] = f.x; v[q * 8 + 2 * i + 1] = f.y; }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = __half2float(src[i]);
+      }
+    } else {
+      const float* src = reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
+      const size_t sr = ((size_t)p.statOff + m) * 2u;
+      const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
+      const float* pv = p.PV + p.pvOff + p.kx0 + k0;
+#pragma unroll
+      for (int i = 0; i < 32; i++) {
+        const float xv = __ldg(src + i);
+        const float t = XMODE == P0P_X_LNMOD ? (xv - mean) * rstd * (1.0f + __ldg(pv + i)) + __ldg(pv + p.pvStride + i) : xv * rstd * __ldg(pv + i);
+        v[i] = __half2float(__float2half_rn(t));          // the prologue's result is an fp16 value (src/ops/gemm.js:66-67)
+      }
+    }
+    float sx = 0.0f, se = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) { sx += v[i]; if (!(i & 1)) se += v[i]; }
+    __half2 o[16];
+    if (ENC == P0P_ENC_Q4) {
+      // per 8 columns: [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16]  (odd nibbles carry 16*q, so their token is pre-divided)
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const float* w = v + 8 * b;
+        o[4 * b + 0] = __floats2half2_rn(w[0], w[4]);
+        o[4 * b + 1] = __floats2half2_rn(w[1] * 0.0625f, w[5] * 0.0625f);
+        o[4 * b + 2] = __floats2half2_rn(w[2], w[6]);
+        o[4 * b + 3] = __floats2half2_rn(w[3] * 0.0625f, w[7] * 0.0625f);
+      }
+      // even nibbles enter as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q
+      cs[m * (d.KC / 32u) + gi] = make_float2(1024.0f * se + 64.0f * (sx - se), sx);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; i++) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      cs[m * (d.KC / 32u) + gi] = make_float2(1152.0f * sx, sx);      // codes enter as 1024 + 128 + q
+    }
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * tok_stride + gi * 64u);
+#pragma unroll
+    for (int q = 0; q < 4; q++) dst[q] = reinterpret_cast<const uint4*>(o)[q];
+  }
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int ENC, int XMODE, int MP>
+__global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const KP& p = d.p;
+  constexpr uint32_t TOK_PAD = ENC == P0P_ENC_Q4 ? 64u : 16u;           // keeps the operand loads free of bank conflicts
+  const uint32_t tok_stride = (d.KC / 32u) * 64u + TOK_PAD;
+  // layout: stages | token tile | (C, Sx) table | barriers
+  unsigned char* stages = smem;
+  unsigned char* xs = stages + D_STAGES * D_STAGE_BYTES;
+  const uint32_t csld = d.KC / 32u;                                    // groups per token in the (C, Sx) table
+  float2* cs = reinterpret_cast<float2*>(xs + ((p.M * tok_stride + 127u) & ~127u));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + ((p.M * csld * sizeof(float2) + 15u) & ~15u));
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + D_STAGES);
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  if (tid == 0) {
+    for (int s = 0; s < D_STAGES; s++) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 4); }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * d.units) / gridDim.x), u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * d.units) / gridDim.x);
+  constexpr uint32_t REC = ENC == P0P_ENC_Q4 ? 1280u : 4224u, REC_K = ENC == P0P_ENC_Q4 ? 32u : 64u;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer: one lane streams the records
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (uint32_t u = u0; u < u1; u++) {
+        const uint32_t kb = u / d.tiles, t = u % d.tiles;
+        const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
+        const uint32_t r0 = d_tile_row0(d, t);
+        const unsigned char* src = p.W + ((size_t)(r0 >> 6) * p.wG + (p.wk0 + k_beg) / REC_K) * REC;
+        for (uint32_t k = 0; k < klen; k += D_STAGE_K, it++) {
+          const uint32_t s = it % D_STAGES, ph = (it / D_STAGES) & 1u;
+          const uint32_t kk = min((uint32_t)D_STAGE_K, klen - k), bytes = (kk / REC_K) * REC;
+          if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, d.status, 101)) return;
+          mbar_expect_tx(full0 + 8u * s, bytes);
+          bulk_g2s(smem_u32(stages + s * D_STAGE_BYTES), src + (size_t)(k / REC_K) * REC, bytes, full0 + 8u * s);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  const uint32_t g = lane >> 2, t4 = lane & 3u;
+  const uint32_t rlo = warp * 16u + g, rhi = rlo + 8u;
+  uint32_t it = 0, cur_kb = 0xffffffffu;
+  bool ok = true;
+  // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
+  // the named barriers below, so nobody is left waiting for it.
+  for (uint32_t u = u0; u < u1; u++) {
+    const uint32_t kb = u / d.tiles, t = u % d.tiles;
+    const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
+    if (kb != cur_kb) {                       // a new k-block: restage the tokens (all consumers are past the old ones)
+      bar_sync_named(1, D_CONSUMERS);
+      if (ok) d_stage_tokens<ENC, XMODE>(d, k_beg, klen, xs, cs, tok_stride, tid);
+      bar_sync_named(1, D_CONSUMERS);
+      cur_kb = kb;
+    }
+    if (!ok) continue;
+    float tot[MP / 8][4];
+#pragma unroll
+    for (int h = 0; h < MP / 8; h++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) tot[h][i] = 0.0f;
+
+    for (uint32_t k = 0; k < klen; k += D_STAGE_K, it++) {
+      const uint32_t s = it % D_STAGES, ph = (it / D_STAGES) & 1u;
+      if (!mbar_wait(full0 + 8u * s, ph, d.status, 102)) { ok = false; break; }
+      const unsigned char* st = stages + s * D_STAGE_BYTES;
+      const uint32_t kk = min((uint32_t)D_STAGE_K, klen - k);
+      if (ENC == P0P_ENC_Q4) {
+#pragma unroll
+        for (uint32_t r = 0; r < D_STAGE_K / 32u; r++) {
+          if (r * 32u >= kk) break;
+          const unsigned char* rec = st + r * 1280u;
+          const uint32_t gi = (k >> 5) + r;
+          const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + rlo * 16u + t4 * 4u), wh = *reinterpret_cast<const uint32_t*>(rec + rhi * 16u + t4 * 4u);
+          const uint32_t sml = *reinterpret_cast<const uint32_t*>(rec + 1024u + rlo * 4u), smh = *reinterpret_cast<const uint32_t*>(rec + 1024u + rhi * 4u);
+          // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
+          const uint32_t l0 = (wl & 0x000f000fu) | 0x64006400u, h0 = (wl & 0x00f000f0u) | 0x64006400u;
+          const uint32_t l1 = ((wl >> 8) & 0x000f000fu) | 0x64006400u, h1 = ((wl >> 8) & 0x00f000f0u) | 0x64006400u;
+          const uint32_t L0 = (wh & 0x000f000fu) | 0x64006400u, H0 = (wh & 0x00f000f0u) | 0x64006400u;
+          const uint32_t L1 = ((wh >> 8) & 0x000f000fu) | 0x64006400u, H1 = ((wh >> 8) & 0x00f000f0u) | 0x64006400u;
+          const float sl = __half2float(__ushort_as_half((unsigned short)(sml & 0xffffu))), ml = __half2float(__ushort_as_half((unsigned short)(sml >> 16)));
+          const float sh = __half2float(__ushort_as_half((unsigned short)(smh & 0xffffu))), mh = __half2float(__ushort_as_half((unsigned short)(smh >> 16)));
+#pragma unroll
+          for (int h = 0; h < MP / 8; h++) {
+            // token columns past M hold zeros; their lanes skip the load (no row of the token tile exists for them)
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (g + 8 * h < p.M) b = *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8 * h) * tok_stride + gi * 64u + t4 * 16u);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma_16816(acc, l0, L0, h0, H0, b.x, b.y);
+            mma_16816(acc, l1, L1, h1, H1, b.z, b.w);
+            const uint32_t ta = min(2u * t4 + 8u * h, p.M - 1u), tb = min(2u * t4 + 1u + 8u * h, p.M - 1u);
+            const float2 c0 = cs[ta * csld + gi], c1 = cs[tb * csld + gi];
+            tot[h][0] = fmaf(ml, c0.y, fmaf(sl, acc[0] - c0.x, tot[h][0]));
+            tot[h][1] = fmaf(ml, c1.y, fmaf(sl, acc[1] - c1.x, tot[h][1]));
+            tot[h][2] = fmaf(mh, c0.y, fmaf(sh, acc[2] - c0.x, tot[h][2]));
+            tot[h][3] = fmaf(mh, c1.y, fmaf(sh, acc[3] - c1.x, tot[h][3]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t r = 0; r < D_STAGE_K / 64u; r++) {
+          if (r * 64u >= kk) break;
+          const unsigned char* rec = st + r * 4224u;
+          const uint32_t gi = (k >> 5) + 2u * r;          // first of the record's two 32-k token groups
+          const uint4 ql = *reinterpret_cast<const uint4*>(rec + rlo * 64u + t4 * 16u), qh = *reinterpret_cast<const uint4*>(rec + rhi * 64u + t4 * 16u);
+          const float sl = __half2float(*reinterpret_cast<const __half*>(rec + 4096u + rlo * 2u)), sh = __half2float(*reinterpret_cast<const __half*>(rec + 4096u + rhi * 2u));
+          const uint32_t wl[4] = {ql.x ^ 0x80808080u, ql.y ^ 0x80808080u, ql.z ^ 0x80808080u, ql.w ^ 0x80808080u};
+          const uint32_t wh[4] = {qh.x ^ 0x80808080u, qh.y ^ 0x80808080u, qh.z ^ 0x80808080u, qh.w ^ 0x80808080u};
+#pragma unroll
+          for (int h = 0; h < MP / 8; h++) {
+            // this lane's 16 columns of the record: 16*t4 .. 16*t4+15, natural order, 32 bytes
+            const unsigned char* bp = xs + (size_t)(g + 8 * h) * tok_stride + gi * 64u + t4 * 32u;
+            uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
+            if (g + 8 * h < p.M) { b0 = *reinterpret_cast<const uint4*>(bp); b1 = *reinterpret_cast<const uint4*>(bp + 16); }
+            const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              mma_16816(acc, __byte_perm(wl[j], 0x64646464u, 0x4140), __byte_perm(wh[j], 0x64646464u, 0x4140),
+                        __byte_perm(wl[j], 0x64646464u, 0x4342), __byte_perm(wh[j], 0x64646464u, 0x4342), bb[2 * j], bb[2 * j + 1]);
+            const uint32_t ta = min(2u * t4 + 8u * h, p.M - 1u), tb = min(2u * t4 + 1u + 8u * h, p.M - 1u);
+            const float2 a0 = cs[ta * csld + gi], a1 = cs[ta * csld + gi + 1];
+            const float2 e0 = cs[tb * csld + gi], e1 = cs[tb * csld + gi + 1];
+            const float C0 = a0.x + a1.x, C1 = e0.x + e1.x;
+            tot[h][0] = fmaf(sl, acc[0] - C0, tot[h][0]);
+            tot[h][1] = fmaf(sl, acc[1] - C1, tot[h][1]);
+            tot[h][2] = fmaf(sh, acc[2] - C0, tot[h][2]);
+            tot[h][3] = fmaf(sh, acc[3] - C1, tot[h][3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8u * s);
+    }
+    if (!ok) continue;
+    // ---- this unit's partial sums: scratch[kb][token][slot]
+#pragma unroll
+    for (int h = 0; h < MP / 8; h++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rhi : rlo;
+        if (tok < p.M) d.scratch[((size_t)kb * p.M + tok) * d.nslots + t * 64u + row] = tot[h][i];
+      }
+    }
+  }
+}
+
+// ---- stage 2: fixed-order sum over the k-blocks, then the fused epilogue.  One block per 128 output columns.
+template <int MP>
+__global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
+  __shared__ float sh[MP * 132];
+  const KP& p = d.p;
+  const uint32_t c = threadIdx.x, nB = blockIdx.x * 128u, col = nB + c;
+  uint32_t slot;
+  if (p.epi == P0P_EPI_SWIGLU) slot = ((col & 1u) ? d.th * 64u : 0u) + (col >> 1);
+  else slot = col;
+  slot = min(slot, d.nslots - 1u);
+  float acc[MP];
+#pragma unroll
+  for (int j = 0; j < MP; j++) {
+    float a = 0.0f;
+    if ((uint32_t)j < p.M) for (uint32_t kb = 0; kb < d.S; kb++) a += d.scratch[((size_t)kb * p.M + j) * d.nslots + slot];
+    acc[j] = a;
+  }
+  epilogue_cols<MP>(p, 0u, nB, c, acc, sh, 1);
+}
+
+inline bool decode_supported(const KP& p) {
+  if (p.M > 16u) return false;
+  if (p.enc != P0P_ENC_Q4 && p.enc != P0P_ENC_Q8) return false;
+  if (p.xmode != P0P_X_F16 && p.xmode != P0P_X_LNMOD && p.xmode != P0P_X_RMS) return false;
+  if (p.wR0 % 64u) return false;
+  if (p.epi == P0P_EPI_SWIGLU && (p.wR1 % 64u)) return false;
+  if (p.K % 128u) return false;                       // a stage is 128 k
+  if ((uintptr_t)p.W & 15u) return false;             // bulk copies need 16-byte aligned sources
+  if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
+  return true;
+}
+
+template <int ENC, int XMODE>
+inline cudaError_t launch_decode_t(const DecodeP& d, int grid, size_t smem, cudaStream_t st) {
+  cudaError_t e;
+  if (d.Mp == 8) {
+    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    k_decode_stream<ENC, XMODE, 8><<<grid, D_THREADS, smem, st>>>(d);
+  } else {
+    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    k_decode_stream<ENC, XMODE, 16><<<grid, D_THREADS, smem, st>>>(d);
+  }
+  return cudaGetLastError();
+}
+
+inline int launch_decode(p0p_ctx* c, const KP& p) {
+  DecodeP d{};
+  d.p = p;
+  d.Mp = p.M <= 8u ? 8u : 16u;
+  const uint32_t cols = p.epi == P0P_EPI_SWIGLU ? p.N / 2u : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u * 128u : p.N);
+  d.th = (cols + 63u) / 64u;
+  // tiles past the weight's last row do not exist: columns there read the last tile (their outputs are never stored)
+  const uint32_t avail = (p.Nw - p.wR0) / 64u;
+  if (p.epi != P0P_EPI_SWIGLU && d.th > avail) d.th = avail;
+  d.tiles = p.epi == P0P_EPI_SWIGLU ? 2u * d.th : d.th;
+  d.nslots = d.tiles * 64u;
+  // k-block: as long as the token tile allows (about 32 KB), short enough for ~4 units per SM
+  const uint32_t sms = (uint32_t)c->prop.multiProcessorCount;
+  uint32_t kc = p.M <= 4u ? 4096u : p.M <= 8u ? 2048u : 1024u;            // token tile of M * kc fp16 stays within 32 KB
+  const uint64_t want_units = 4ull * sms;
+  while (kc > 256u && (uint64_t)d.tiles * ((p.K + kc - 1u) / kc) < want_units) kc >>= 1;
+  if (kc > p.K) kc = p.K;
+  d.KC = kc; d.S = (p.K + kc - 1u) / kc; d.units = d.tiles * d.S;
+  const uint64_t sbytes = (uint64_t)d.S * p.M * d.nslots * 4ull;
+  if (int r = ensure_scratch(c, sbytes + 256)) return r;
+  d.scratch = reinterpret_cast<float*>(c->scratch);
+  d.status = c->dev_status;
+  const uint32_t tok_stride = (d.KC / 32u) * 64u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
+  const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES + ((p.M * tok_stride + 127u) & ~127u) + (((size_t)p.M * (d.KC / 32u) * 8u + 15u) & ~15u) + 2u * D_STAGES * 8u + 128u;
+  const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (size_t)(c->prop.sharedMemPerMultiprocessor) / (smem + 1024)));
+  const int grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * sms);      // every block is resident: the unit ranges run side by side
+  cudaError_t e;
+  if (p.enc == P0P_ENC_Q4) {
+    if (p.xmode == P0P_X_F16) e = launch_decode_t<P0P_ENC_Q4, P0P_X_F16>(d, grid, smem, c->stream);
+    else if (p.xmode == P0P_X_RMS) e = launch_decode_t<P0P_ENC_Q4, P0P_X_RMS>(d, grid, smem, c->stream);
+    else e = launch_decode_t<P0P_ENC_Q4, P0P_X_LNMOD>(d, grid, smem, c->stream);
+  } else {
+    if (p.xmode == P0P_X_F16) e = launch_decode_t<P0P_ENC_Q8, P0P_X_F16>(d, grid, smem, c->stream);
+    else if (p.xmode == P0P_X_RMS) e = launch_decode_t<P0P_ENC_Q8, P0P_X_RMS>(d, grid, smem, c->stream);
+    else e = launch_decode_t<P0P_ENC_Q8, P0P_X_LNMOD>(d, grid, smem, c->stream);
+  }
+  if (e != cudaSuccess) return cuda_fail(c, e, "decode launch");
+  const uint32_t fin_cols = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u : (((p.N + 3u) & ~3u) + 127u) / 128u;
+  if (d.Mp == 8) k_decode_finish<8><<<fin_cols, 128, 0, c->stream>>>(d);
+  else k_decode_finish<16><<<fin_cols, 128, 0, c->stream>>>(d);
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "decode finish launch");
+  c->launches += 2;
+  return 0;
+}
+
+}  // namespace p0p

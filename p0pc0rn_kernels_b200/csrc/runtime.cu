@@ -23,10 +23,25 @@ int p0p_open(int device, const p0p_opts* opts, p0p_ctx** out) {
   DeviceGuard g(device);
   if ((e = cudaGetDeviceProperties(&c->prop, device)) != cudaSuccess) { delete c; return (int)e; }
   if (c->prop.major < 10) { delete c; return -3; }   // sm_100a code only: the analogue of the missing 'shader-f16' feature (src/core/gpu.js:49)
-  if (opts && opts->struct_size >= sizeof(p0p_opts) && opts->stream) { c->stream = (cudaStream_t)opts->stream; c->own_stream = false; }
+  if (opts && opts->struct_size >= sizeof(p0p_opts) && (opts->flags & P0P_OPT_USE_STREAM)) { c->stream = (cudaStream_t)opts->stream; c->own_stream = false; }
   else if ((e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)) != cudaSuccess) { delete c; return (int)e; }
   if ((e = cudaEventCreateWithFlags(&c->ev, cudaEventDisableTiming)) != cudaSuccess) { if (c->own_stream) cudaStreamDestroy(c->stream); delete c; return (int)e; }
+  if ((e = cudaHostAlloc((void**)&c->host_status, sizeof(int), cudaHostAllocMapped)) != cudaSuccess ||
+      (e = cudaHostGetDevicePointer((void**)&c->dev_status, c->host_status, 0)) != cudaSuccess) {
+    if (c->host_status) cudaFreeHost(c->host_status);
+    cudaEventDestroy(c->ev); if (c->own_stream) cudaStreamDestroy(c->stream); delete c; return (int)e;
+  }
+  *c->host_status = 0;
   *out = c;
+  return 0;
+}
+
+// after a stream sync: did a kernel give up on a bounded wait?
+static int check_kernel_status(p0p_ctx* c) {
+  if (c->host_status && *c->host_status) {
+    int code = *c->host_status; *c->host_status = 0;
+    return fail(c, -10, "a kernel gave up on a bounded wait (code %d); results of the queued work are invalid", code);
+  }
   return 0;
 }
 
@@ -58,6 +73,7 @@ int p0p_close(p0p_ctx* c) {
   c->bufs.clear();
   evict(c, 0);
   if (c->scratch) cudaFree(c->scratch);
+  if (c->host_status) cudaFreeHost(c->host_status);
   for (void* p : c->pinned) cudaFreeHost(p);
   cudaStreamSynchronize(c->stream);
   if (c->ev) cudaEventDestroy(c->ev);
@@ -181,7 +197,7 @@ int p0p_read(p0p_ctx* c, const p0p_buf* b, uint64_t off, void* host, uint64_t by
   DeviceGuard g(c->device);
   P0P_CUDA(c, cudaMemcpyAsync(host, (const char*)b->ptr + off, bytes, cudaMemcpyDeviceToHost, c->stream), "read");
   P0P_CUDA(c, cudaStreamSynchronize(c->stream), "read");
-  return 0;
+  return check_kernel_status(c);
 }
 
 int p0p_clear(p0p_ctx* c, p0p_buf* b, uint64_t off, uint64_t bytes) {
@@ -205,7 +221,7 @@ int p0p_sync(p0p_ctx* c) {
   P0P_ALIVE(c);
   DeviceGuard g(c->device);
   P0P_CUDA(c, cudaStreamSynchronize(c->stream), "done");
-  return 0;
+  return check_kernel_status(c);
 }
 
 int p0p_host_alloc(p0p_ctx* c, uint64_t bytes, void** out) {

@@ -75,7 +75,8 @@ class Gpu:
         self.tune = None
         self.calib = None
         self._h = C.c_void_p()
-        o = Opts(C.sizeof(Opts), 0, self.opts.get("stream"))
+        has_stream = "stream" in self.opts and self.opts["stream"] is not None
+        o = Opts(C.sizeof(Opts), 1 if has_stream else 0, self.opts.get("stream") if has_stream else None)
         rc = lib.p0p_open(int(self.opts["device"]), C.byref(o), C.byref(self._h))
         if rc:
             raise GpuError({-2: "no such CUDA device", -3: "an sm_100 (B200) device is required"}.get(rc, f"no CUDA device (error {rc})"))

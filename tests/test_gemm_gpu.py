@@ -236,6 +236,46 @@ def test_fused_variants(gpu, oracle, case, kernel):
     CS.check(got, want, case["name"])
 
 
+DECODE = [
+    dict(name="d q4 M1", enc="q4", M=1, N=256, K=512),
+    dict(name="d q8 M1", enc="q8", M=1, N=256, K=512),
+    dict(name="d q4 M2 long K", enc="q4", M=2, N=128, K=4096 + 1024),
+    dict(name="d q8 M3 long K", enc="q8", M=3, N=192, K=4096 + 384),
+    dict(name="d q4 M5 K384", enc="q4", M=5, N=320, K=384),
+    dict(name="d q4 M8", enc="q4", M=8, N=512, K=1024),
+    dict(name="d q8 M9", enc="q8", M=9, N=256, K=640),
+    dict(name="d q4 M16", enc="q4", M=16, N=1024, K=2048),
+    dict(name="d q8 M16", enc="q8", M=16, N=256, K=1536),
+    dict(name="d q4 M13 tail cols", enc="q4", M=13, N=100, K=256, w_rows=128),
+    dict(name="d rms+swiglu M1", enc="q4", M=1, N=512, K=1024, xmode="rms", epi="swiglu"),
+    dict(name="d rms+swiglu M16 rows", enc="q4", M=16, N=256, K=512, xmode="rms", epi="swiglu", bias=True, wr0=64, wr1=256, w_rows=448, st_off=2, pv_off=4),
+    dict(name="d geglu q8 M4", enc="q8", M=4, N=256, K=256, epi="swiglu", act="gelu"),
+    dict(name="d resadd M1", enc="q4", M=1, N=256, K=1024, epi="resadd"),
+    dict(name="d resadd gate+bias M7", enc="q8", M=7, N=192, K=256, epi="resadd", gate=True, bias=True, ev_off=8, bv_off=4),
+    dict(name="d f32 M3", enc="q4", M=3, N=128, K=256, epi="f32"),
+    dict(name="d bias+res M6", enc="q4", M=6, N=128, K=256, epi="bias", res=True),
+    dict(name="d lnmod+heads M12", enc="q8", M=12, N=384, K=256, xmode="lnmod", epi="heads", heads=dict(Ltot=20, Hq=1, Hkv=1, rowOff=3, eps=1e-6)),
+    dict(name="d heads half M5", enc="q4", M=5, N=512, K=256, epi="heads", heads=dict(Ltot=8, Hq=2, Hkv=1, rowOff=1, eps=1e-6, ropeMode="half")),
+    dict(name="d onormgate M4", enc="q4", M=4, N=256, K=256, epi="onormgate", Ltot=256),
+    dict(name="d sub-ranges M4", enc="q4", M=4, N=128, K=128, ldx=320, kx0=64, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="d sub-ranges q8 M4", enc="q8", M=4, N=128, K=128, ldx=328, kx0=66, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="d byte offsets M2", enc="q8", M=2, N=128, K=128, x_off=256, w_off=512, y_off=768),
+]
+
+
+@pytest.mark.parametrize("case", DECODE, ids=lambda c: c["name"])
+def test_decode_kernel(gpu, oracle, case):
+    """the decode-sized kernel (M <= 16: bulk-copy weight stream, raw codes on the tensor cores, split-K) against the oracle"""
+    from p0pc0rn_kernels_b200._lib import K_DECODE
+    h = CS.build(dict(case, kernel="decode"))
+    got = CS.run_gpu(gpu, h)
+    assert gpu.lastKernel == K_DECODE
+    CS.check(got, CS.run_oracle(h), case["name"])
+    h2 = CS.build(dict(case))                                   # and it is what the library picks by itself
+    got2 = CS.run_gpu(gpu, h2)
+    assert gpu.lastKernel == K_DECODE and np.array_equal(got, got2), "not deterministic run to run"
+
+
 @pytest.mark.parametrize("enc,scale", [("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q4g32a.t64", "offset"), ("f16", 0.05)])
 @pytest.mark.parametrize("path", [0, 1])
 def test_dequant_bit_exact(gpu, oracle, enc, scale, path):
