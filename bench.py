@@ -141,6 +141,54 @@ def run_reference(args, rank):
                       "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
+def run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world):
+    """Plain GEMMs (no prologue, fp16 store) of given shapes, N-sharded over the ranks (no gather): one JSON line per
+    shape with TFLOP/s, GB/s of the algorithmic bytes and both roofline fractions.  Weights are rotated so that
+    every launch streams from HBM."""
+    if args.sweep:
+        shapes = [(e, m, n, k) for e in ("q4", "q8") for (n, k) in ((4096, 4096), (14336, 4096), (4096, 14336), (16384, 16384)) for m in (1, 16, 128, 1024, 8192)]
+    else:
+        shapes = [(t.split(":")[0], int(t.split(":")[1]), int(t.split(":")[2]), int(t.split(":")[3])) for t in args.shape.split(",")]
+    rs = np.random.default_rng(7)
+    for enc, M, N, K in shapes:
+        encn = {"q4": "q4g32a.t64", "q8": "q8g64s.t64", "f16": "f16"}[enc]
+        nl = N // world
+        slab_rows = min(nl, 1024)
+        W0 = (rs.standard_normal(slab_rows * K) * 0.02).astype(np.float32)
+        slab = P.packQ4(W0, slab_rows, K) if enc == "q4" else P.packQ8(W0, slab_rows, K) if enc == "q8" else P.packF16(W0)
+        wbytes = np.tile(slab, -(-nl // slab_rows))[: P.encodedBytes(encn, nl, K)]
+        copies = max(2, min(8, int(np.ceil(300e6 / wbytes.nbytes))))
+        Ws = [gpu.upload(wbytes) for _ in range(copies)]
+        xb = gpu.upload(P.toF16(rs.standard_normal(M * K).astype(np.float32))); yb = gpu.buffer(M * nl * 2)
+        def call(i):
+            a = {"w": {"enc": encn, "buf": Ws[i], "off": 0, "bytes": wbytes.nbytes, "rows": nl, "cols": K}, "x": {"buf": xb}, "y": {"buf": yb}, "M": M, "N": nl, "K": K}
+            if args.kernel: a["kernel"] = args.kernel
+            P.gemm(gpu, a)
+        gs = []
+        for i in range(copies):
+            call(i); call(i); torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream): call(i)
+            gs.append(g)
+        fam = P._lib.KERNEL_NAMES.get(gpu.lastKernel)
+        reps = max(args.steps, 10)
+        for s in range(max(3, args.warmup)): gs[s % copies].replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(reps): gs[s % copies].replay()
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        fl = 2.0 * M * nl * K; by = wbytes.nbytes + M * K * 2 + M * nl * 2
+        if rank == 0:
+            print(json.dumps({"shape": {"enc": enc, "M": M, "N": N, "K": K, "n_gpus": world}, "family": fam, "ms": ms, "TFLOP/s": fl * world / (ms * 1e-3) / 1e12,
+                              "GB/s": by * world / (ms * 1e-3) / 1e9, "frac_hbm": by / (ms * 1e-3) / 1e9 / pk["hbm"], "frac_tensor": fl / (ms * 1e-3) / 1e12 / pk["tensor"],
+                              "weight_copies": copies}), flush=True)
+        for b in Ws + [xb, yb]: gpu.free(b)
+        gpu.drainPool()
+    gpu.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -151,6 +199,8 @@ def main():
     ap.add_argument("--copies", type=int, default=3, help="weight copies rotated through so that every step streams from HBM")
     ap.add_argument("--skip-cases", action="store_true", help="only the headline (for profiler captures)")
     ap.add_argument("--kernel", default=None, help="force a kernel family (generic | decode | umma)")
+    ap.add_argument("--shape", default=None, help="enc:M:N:K[,enc:M:N:K...]  time plain GEMMs of these shapes instead of the block (q4|q8|f16)")
+    ap.add_argument("--sweep", action="store_true", help="the large-shape sweep of the baseline's configs (q4/q8, M in 1..8192, four (N,K))")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -170,6 +220,9 @@ def main():
     torch.cuda.set_stream(stream)
     gpu = P.createGpu({"device": local, "stream": stream.cuda_stream})
     pk = peaks()
+
+    if args.shape or args.sweep:
+        return run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world)
 
     # ---- model state: this rank's column shard of both weights (the whole weights at N = 1), `copies` times
     ffl, hidl = FF // world, HID // world
@@ -213,42 +266,64 @@ def main():
             xv = x_t[: M * HID].view(M, HID)
             xv.copy_(P.all_gather_columns(xv[:, rank * hidl:(rank + 1) * hidl]))
 
+    def graphs_of(fn):
+        """one CUDA graph per weight copy holding the launches fn(i) makes (launch-bound steps would otherwise time the host)"""
+        gs = []
+        for i in range(args.copies):
+            fn(i); fn(i)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn(i)
+            gs.append(g)
+        return gs
+
     def timed(M, steps, warmup, gather=True):
-        for s in range(warmup): block(M, s % args.copies, gather)
+        """exactly `steps` steps (graph replays, rotating the weight copies), device time, max over ranks"""
+        l0 = gpu.launches
+        block(M, 0, gather)
+        per_step = gpu.launches - l0
+        gs = graphs_of(lambda i: block(M, i, gather))
+        for s in range(warmup): gs[s % args.copies].replay()
         torch.cuda.synchronize()
         if world > 1: dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = gpu.launches
         e0.record()
-        for s in range(steps): block(M, s % args.copies, gather)
+        for s in range(steps): gs[s % args.copies].replay()
         e1.record()
         torch.cuda.synchronize()
         if world > 1: dist.barrier()
         ms = e0.elapsed_time(e1)
-        launches["n"] = gpu.launches - l0
+        launches["n"] = per_step * steps
         if world > 1:
             t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
         return ms / steps
 
+    def one_gemm(M, which, i):
+        if which == "gate_up":
+            a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
+                 "y": {"buf": hl, "ld": ffl}, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
+        else:
+            a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
+                 "y": {"buf": xb, "ld": HID, "n0": rank * hidl}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
+        if args.kernel: a["kernel"] = args.kernel
+        P.gemm(gpu, a)
+
     def kernel_ms(M, which, reps):
-        """average device time of ONE kernel of the block (gate/up or down), CUDA events around each launch"""
-        evs = []
-        for s in range(reps + 2):
-            i = s % args.copies
-            P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
-            if which == "gate_up":
-                a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
-                     "y": {"buf": hl, "ld": ffl}, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
-            else:
-                a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
-                     "y": {"buf": xb, "ld": HID, "n0": rank * hidl}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
-            if args.kernel: a["kernel"] = args.kernel
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); P.gemm(gpu, a); e1.record()
-            evs.append((e0, e1))
+        """average device time of ONE gemm call of the block (gate/up or down): graphs of that call alone, replayed
+        back to back over the rotating weight copies, CUDA events around the run"""
+        P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
+        gs = graphs_of(lambda i: one_gemm(M, which, i))
+        fam = gpu.lastKernel
+        for s in range(3): gs[s % args.copies].replay()
         torch.cuda.synchronize()
-        return float(np.mean([a.elapsed_time(b) for a, b in evs[2:]])), gpu.lastKernel
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(reps): gs[s % args.copies].replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps, fam
 
     # ---- headline: K timed steps at M = args.m
     M = args.m
@@ -256,7 +331,7 @@ def main():
     if rank == 0: sampler.start()
     ms = timed(M, args.steps, max(3, args.warmup))
     n_launch = launches["n"]
-    gu_ms, gu_kernel = kernel_ms(M, "gate_up", min(20, args.steps))
+    gu_ms, gu_kernel = kernel_ms(M, "gate_up", max(20, min(100, args.steps)))
     clocks = sampler.stop() if rank == 0 else None
     value = block_flops(M) / (ms * 1e-3) / 1e12
 
@@ -291,10 +366,13 @@ def main():
         for Mc in (1, 16):
             msc = timed(Mc, max(20, args.steps), 5, gather=True)
             gbs = block_bytes(Mc) / world / (msc * 1e-3) / 1e9 if world > 1 else block_bytes(Mc) / (msc * 1e-3) / 1e9
-            kms, kk = kernel_ms(Mc, "gate_up", 20)
+            kms, kk = kernel_ms(Mc, "gate_up", 60)
+            dms, _ = kernel_ms(Mc, "down", 60)
+            db = (hidl * FF * 5 // 8) + Mc * FF * 2 + 2 * Mc * hidl * 4
             kb = (2 * ffl * HID * 5 // 8) + Mc * HID * 4 + Mc * ffl * 2
             cases.append({"M": Mc, "ms_per_step": msc, "GB/s": gbs * (world if world > 1 else 1), "TFLOP/s": block_flops(Mc) / (msc * 1e-3) / 1e12,
-                          "gate_up_kernel": {"ms": kms, "GB/s": kb / (kms * 1e-3) / 1e9, "frac_hbm": kb / (kms * 1e-3) / 1e9 / pk["hbm"], "family": P._lib.KERNEL_NAMES.get(kk)}})
+                          "gate_up_kernel": {"ms": kms, "GB/s": kb / (kms * 1e-3) / 1e9, "frac_hbm": kb / (kms * 1e-3) / 1e9 / pk["hbm"], "family": P._lib.KERNEL_NAMES.get(kk)},
+                          "down_kernel": {"ms": dms, "GB/s": db / (dms * 1e-3) / 1e9, "frac_hbm": db / (dms * 1e-3) / 1e9 / pk["hbm"]}})
 
     # ---- roofline of the dominant kernel (gate/up GEMM: 2/3 of the block's FLOPs)
     gu_flops = 2.0 * M * (2 * ffl) * HID

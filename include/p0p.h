@@ -98,6 +98,17 @@ int p0p_sync(p0p_ctx* ctx);
 int p0p_host_alloc(p0p_ctx* ctx, uint64_t bytes, void** out);
 int p0p_host_free(p0p_ctx* ctx, void* p);
 
+/* ---- recorded launch sequences ---------------------------------------------------------------------------- */
+/* The reference's Runner batches dispatches into one command buffer per submit (src/core/gpu.js:203-257) to keep
+ * the GPU fed; the CUDA analogue is a graph.  Between begin and end, p0p_gemm / p0p_rowstats / p0p_copy /
+ * p0p_clear calls are recorded instead of run; p0p_graph_launch replays them in stream order.  Run the same
+ * calls once before recording (first calls size the library's scratch memory). */
+typedef struct p0p_graph p0p_graph;
+int p0p_capture_begin(p0p_ctx* ctx);
+int p0p_capture_end(p0p_ctx* ctx, p0p_graph** out);
+int p0p_graph_launch(p0p_ctx* ctx, p0p_graph* g);
+int p0p_graph_free(p0p_ctx* ctx, p0p_graph* g);
+
 /* ---- the op -------------------------------------------------------------------------------------------- */
 /* The uniform block of the reference shader (struct P, src/ops/gemm.js:39-41, filled at :317-322) plus the
  * bindings (:304-313) and the configuration key (:275-277).  Offsets are in the unit the reference uses:

@@ -1,7 +1,7 @@
 """p0pc0rn-kernels `gemm` for B200: hand-written sm_100a CUDA kernels behind the reference's ``op(gpu, args)`` API.
 
 The names exported here are the reference's (src/index.js) for the gemm path and the model I/O either side of it.
-The native library must be built (``python -m p0pc0rn_kernels_b200.build``); there is no CPU fallback."""
+The native library must be built (``python p0pc0rn_kernels_b200/build.py``); there is no CPU fallback."""
 from .convert import ALIGN, convert, convertSafetensors, encodedBytes, writeSafetensors
 from .encode import (MANIFEST_FORMAT, chooseEncoding, dtypeBytes, encodeRows, matrixOf, packF16, packF32, packQ4, packQ8, reorderConvRows,
                      safetensorsHeader, safetensorsList, tileBytes, toFloat32)

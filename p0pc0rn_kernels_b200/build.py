@@ -1,5 +1,9 @@
 """Builds the native library of this package in-tree: ``libp0p.so`` (CUDA kernels for sm_100a + the C ABI of
-``include/p0p.h``).  nvcc cross-compiles without a GPU."""
+``include/p0p.h``).  nvcc cross-compiles without a GPU.
+
+    python p0pc0rn_kernels_b200/build.py [--force]
+
+Run it as a script (or load it by path): importing the package needs the library this builds."""
 from __future__ import annotations
 
 import os

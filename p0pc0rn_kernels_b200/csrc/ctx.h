@@ -36,6 +36,7 @@ struct p0p_ctx {
   // split-K partial sums of the decode kernel (grown on demand, owned by the context)
   void* scratch = nullptr;
   uint64_t scratch_bytes = 0;
+  bool capturing = false;
   std::unordered_set<void*> pinned;
   // a host-visible word kernels write when a bounded wait runs out (0 = fine)
   int* host_status = nullptr;

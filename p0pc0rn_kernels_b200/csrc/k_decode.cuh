@@ -32,6 +32,7 @@ constexpr int D_STAGES = 6;
 constexpr int D_STAGE_K = 128;              // k per stage: 4 q4 records (5120 B) or 2 q8 records (8448 B)
 constexpr int D_STAGE_BYTES = 8448;
 constexpr int D_MAX_KC = 4096;              // largest k-block
+constexpr int D_SMEM_MAX = 112 * 1024;      // dynamic shared memory ceiling of the stream kernel
 
 struct DecodeP {
   KP p;
@@ -51,71 +52,90 @@ __device__ __forceinline__ uint32_t d_tile_row0(const DecodeP& d, uint32_t t) {
   return d.p.wR0 + t * 64u;
 }
 
-// ---- token staging: one thread per (token, 32-k group).  Writes the group's 64 bytes in operand order and
-// its (C, Sx) pair.
-template <int ENC, int XMODE>
-__device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float2* cs, uint32_t tok_stride, uint32_t tid) {
+// ---- token staging: one thread per (token, scale group: 32 k for q4, 64 k for q8).  Writes the group's tokens in
+// operand order and its correction terms.
+//   q4: ct[gi][token pair] = float4(-C_a, Sx_a, -C_b, Sx_b),  C = 1024 * sum(x, even k) + 64 * sum(x, odd k)
+//   q8: ct[gi][token pair] = float2(-C_a, -C_b),              C = 1152 * sum(x)
+template <int ENC, int XMODE, int MP>
+__device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float* ct, uint32_t tok_stride, uint32_t tid) {
   const KP& p = d.p;
-  const uint32_t groups = klen / 32u;
+  constexpr uint32_t GS = ENC == P0P_ENC_Q4 ? 32u : 64u;
+  const uint32_t groups = klen / GS;
   for (uint32_t it = tid; it < p.M * groups; it += D_CONSUMERS) {
-    const uint32_t m = it / groups, gi = it % groups, k0 = kb0 + gi * 32u;
-    float v[32];
-    if (XMODE == P0P_X_F16) {
-      const __half* src = reinterpret_cast<const __half*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
-      if (p.vecx) {
+    const uint32_t m = it / groups, gi = it % groups, k0 = kb0 + gi * GS;
+    float sx = 0.0f, se = 0.0f;
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
-          const __half2* h = reinterpret_cast<const __half2*>(&u);
+    for (uint32_t part = 0; part < GS / 32u; part++) {
+      float v[32];
+      if (XMODE == P0P_X_F16) {
+        const __half* src = reinterpret_cast<const __half*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0 + part * 32u;
+        if (p.vecx) {
 #pragma unroll
-          for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); v[q * 8 + 2 * i] = f.x; v[q * 8 + 2 * i + 1] = f.y; }
+          for (int q = 0; q < 4; q++) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); v[q * 8 + 2 * i] = f.x; v[q * 8 + 2 * i + 1] = f.y; }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) v[i] = __half2float(src[i]);
+        }
+      } else {
+        const float* src = reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0 + part * 32u;
+        const size_t sr = ((size_t)p.statOff + m) * 2u;
+        const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
+        const float* pv = p.PV + p.pvOff + p.kx0 + k0 + part * 32u;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const float xv = __ldg(src + i);
+          const float t = XMODE == P0P_X_LNMOD ? (xv - mean) * rstd * (1.0f + __ldg(pv + i)) + __ldg(pv + p.pvStride + i) : xv * rstd * __ldg(pv + i);
+          v[i] = __half2float(__float2half_rn(t));          // the prologue's result is an fp16 value (src/ops/gemm.js:66-67)
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i++) { sx += v[i]; if (!(i & 1)) se += v[i]; }
+      __half2 o[16];
+      if (ENC == P0P_ENC_Q4) {
+        // per 8 columns: [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16]  (odd nibbles carry 16*q, so their token is pre-divided)
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          const float* w = v + 8 * b;
+          o[4 * b + 0] = __floats2half2_rn(w[0], w[4]);
+          o[4 * b + 1] = __floats2half2_rn(w[1] * 0.0625f, w[5] * 0.0625f);
+          o[4 * b + 2] = __floats2half2_rn(w[2], w[6]);
+          o[4 * b + 3] = __floats2half2_rn(w[3] * 0.0625f, w[7] * 0.0625f);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = __half2float(src[i]);
+        for (int i = 0; i < 16; i++) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
       }
-    } else {
-      const float* src = reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
-      const size_t sr = ((size_t)p.statOff + m) * 2u;
-      const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
-      const float* pv = p.PV + p.pvOff + p.kx0 + k0;
+      uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * tok_stride + (k0 - kb0 + part * 32u) * 2u);
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        const float xv = __ldg(src + i);
-        const float t = XMODE == P0P_X_LNMOD ? (xv - mean) * rstd * (1.0f + __ldg(pv + i)) + __ldg(pv + p.pvStride + i) : xv * rstd * __ldg(pv + i);
-        v[i] = __half2float(__float2half_rn(t));          // the prologue's result is an fp16 value (src/ops/gemm.js:66-67)
-      }
+      for (int q = 0; q < 4; q++) dst[q] = reinterpret_cast<const uint4*>(o)[q];
     }
-    float sx = 0.0f, se = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 32; i++) { sx += v[i]; if (!(i & 1)) se += v[i]; }
-    __half2 o[16];
     if (ENC == P0P_ENC_Q4) {
-      // per 8 columns: [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16]  (odd nibbles carry 16*q, so their token is pre-divided)
-#pragma unroll
-      for (int b = 0; b < 4; b++) {
-        const float* w = v + 8 * b;
-        o[4 * b + 0] = __floats2half2_rn(w[0], w[4]);
-        o[4 * b + 1] = __floats2half2_rn(w[1] * 0.0625f, w[5] * 0.0625f);
-        o[4 * b + 2] = __floats2half2_rn(w[2], w[6]);
-        o[4 * b + 3] = __floats2half2_rn(w[3] * 0.0625f, w[7] * 0.0625f);
-      }
-      // even nibbles enter as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q
-      cs[m * (d.KC / 32u) + gi] = make_float2(1024.0f * se + 64.0f * (sx - se), sx);
+      // even nibbles enter the multiply as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q
+      float* c = ct + ((size_t)gi * (MP / 2) + (m >> 1)) * 4u + (m & 1u) * 2u;
+      c[0] = -(1024.0f * se + 64.0f * (sx - se)); c[1] = sx;
     } else {
-#pragma unroll
-      for (int i = 0; i < 16; i++) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-      cs[m * (d.KC / 32u) + gi] = make_float2(1152.0f * sx, sx);      // codes enter as 1024 + 128 + q
+      ct[((size_t)gi * (MP / 2) + (m >> 1)) * 2u + (m & 1u)] = -1152.0f * sx;        // codes enter as 1024 + 128 + q
     }
-    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * tok_stride + gi * 64u);
-#pragma unroll
-    for (int q = 0; q < 4; q++) dst[q] = reinterpret_cast<const uint4*>(o)[q];
   }
 }
 
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// (a & mask) | magic in ONE instruction (left to the compiler this becomes two)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));
+  return d;
+}
+
+// D = A * B + C with C given separately (the correction terms ride in on C)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, const float (&c)[4]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
 template <int ENC, int XMODE, int MP>
@@ -123,13 +143,14 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   extern __shared__ __align__(128) unsigned char smem[];
   const KP& p = d.p;
   constexpr uint32_t TOK_PAD = ENC == P0P_ENC_Q4 ? 64u : 16u;           // keeps the operand loads free of bank conflicts
-  const uint32_t tok_stride = (d.KC / 32u) * 64u + TOK_PAD;
-  // layout: stages | token tile | (C, Sx) table | barriers
+  constexpr uint32_t GS = ENC == P0P_ENC_Q4 ? 32u : 64u;
+  constexpr uint32_t CT_F = ENC == P0P_ENC_Q4 ? 4u : 2u;                // floats per (group, token pair) in the correction table
+  const uint32_t tok_stride = d.KC * 2u + TOK_PAD;
+  // layout: stages | token tile | correction table | barriers
   unsigned char* stages = smem;
   unsigned char* xs = stages + D_STAGES * D_STAGE_BYTES;
-  const uint32_t csld = d.KC / 32u;                                    // groups per token in the (C, Sx) table
-  float2* cs = reinterpret_cast<float2*>(xs + ((p.M * tok_stride + 127u) & ~127u));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + ((p.M * csld * sizeof(float2) + 15u) & ~15u));
+  float* ct = reinterpret_cast<float*>(xs + ((p.M * tok_stride + 127u) & ~127u));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ct) + (d.KC / GS) * (MP / 2) * CT_F * 4u);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + D_STAGES);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -141,22 +162,22 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 
   const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * d.units) / gridDim.x), u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * d.units) / gridDim.x);
   constexpr uint32_t REC = ENC == P0P_ENC_Q4 ? 1280u : 4224u, REC_K = ENC == P0P_ENC_Q4 ? 32u : 64u;
+  constexpr uint32_t STAGE_TX = (D_STAGE_K / REC_K) * REC;              // a k-block is a whole number of stages (K % 128 == 0)
 
   if (warp == 4) {
     // ------------------------------------------------------------------ producer: one lane streams the records
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, ph = 0;
       for (uint32_t u = u0; u < u1; u++) {
         const uint32_t kb = u / d.tiles, t = u % d.tiles;
         const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
         const uint32_t r0 = d_tile_row0(d, t);
         const unsigned char* src = p.W + ((size_t)(r0 >> 6) * p.wG + (p.wk0 + k_beg) / REC_K) * REC;
-        for (uint32_t k = 0; k < klen; k += D_STAGE_K, it++) {
-          const uint32_t s = it % D_STAGES, ph = (it / D_STAGES) & 1u;
-          const uint32_t kk = min((uint32_t)D_STAGE_K, klen - k), bytes = (kk / REC_K) * REC;
+        for (uint32_t k = 0; k < klen; k += D_STAGE_K, src += STAGE_TX) {
           if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, d.status, 101)) return;
-          mbar_expect_tx(full0 + 8u * s, bytes);
-          bulk_g2s(smem_u32(stages + s * D_STAGE_BYTES), src + (size_t)(k / REC_K) * REC, bytes, full0 + 8u * s);
+          mbar_expect_tx(full0 + 8u * s, STAGE_TX);
+          bulk_g2s(smem_u32(stages + s * D_STAGE_BYTES), src, STAGE_TX, full0 + 8u * s);
+          if (++s == D_STAGES) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -165,8 +186,16 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 
   // -------------------------------------------------------------------- consumers
   const uint32_t g = lane >> 2, t4 = lane & 3u;
-  const uint32_t rlo = warp * 16u + g, rhi = rlo + 8u;
-  uint32_t it = 0, cur_kb = 0xffffffffu;
+  const uint32_t rlo = warp * 16u + g;                                   // this lane's rows: rlo and rlo + 8
+  // byte offsets that stay fixed for the whole kernel
+  const uint32_t code_off = ENC == P0P_ENC_Q4 ? rlo * 16u + t4 * 4u : rlo * 64u + t4 * 16u;
+  const uint32_t sm_off = ENC == P0P_ENC_Q4 ? 1024u + rlo * 4u : 4096u + rlo * 2u;
+  const bool tok0 = g < p.M, tok1 = g + 8u < p.M;                        // does this lane's token column exist?
+  const unsigned char* xrow0 = xs + (size_t)g * tok_stride + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
+  const unsigned char* xrow1 = xrow0 + 8u * (size_t)tok_stride;
+  const float* ctl = ct + t4 * CT_F;                                     // this lane's token pair (2 t4, 2 t4 + 1); + 4 pairs for tokens 8..15
+  uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
+  const uint32_t MLO = 0x000f000fu, MHI = 0x00f000f0u, MAGIC = 0x64006400u;
   bool ok = true;
   // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
   // the named barriers below, so nobody is left waiting for it.
@@ -175,7 +204,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
     if (kb != cur_kb) {                       // a new k-block: restage the tokens (all consumers are past the old ones)
       bar_sync_named(1, D_CONSUMERS);
-      if (ok) d_stage_tokens<ENC, XMODE>(d, k_beg, klen, xs, cs, tok_stride, tid);
+      if (ok) d_stage_tokens<ENC, XMODE, MP>(d, k_beg, klen, xs, ct, tok_stride, tid);
       bar_sync_named(1, D_CONSUMERS);
       cur_kb = kb;
     }
@@ -186,77 +215,74 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 #pragma unroll
       for (int i = 0; i < 4; i++) tot[h][i] = 0.0f;
 
-    for (uint32_t k = 0; k < klen; k += D_STAGE_K, it++) {
-      const uint32_t s = it % D_STAGES, ph = (it / D_STAGES) & 1u;
+    for (uint32_t k = 0; k < klen; k += D_STAGE_K) {
       if (!mbar_wait(full0 + 8u * s, ph, d.status, 102)) { ok = false; break; }
       const unsigned char* st = stages + s * D_STAGE_BYTES;
-      const uint32_t kk = min((uint32_t)D_STAGE_K, klen - k);
+      const unsigned char* xk0 = xrow0 + k * 2u;
+      const unsigned char* xk1 = xrow1 + k * 2u;
+      const float* ck = ctl + (k / GS) * (MP / 2) * CT_F;
       if (ENC == P0P_ENC_Q4) {
 #pragma unroll
         for (uint32_t r = 0; r < D_STAGE_K / 32u; r++) {
-          if (r * 32u >= kk) break;
           const unsigned char* rec = st + r * 1280u;
-          const uint32_t gi = (k >> 5) + r;
-          const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + rlo * 16u + t4 * 4u), wh = *reinterpret_cast<const uint32_t*>(rec + rhi * 16u + t4 * 4u);
-          const uint32_t sml = *reinterpret_cast<const uint32_t*>(rec + 1024u + rlo * 4u), smh = *reinterpret_cast<const uint32_t*>(rec + 1024u + rhi * 4u);
+          const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + code_off), wh = *reinterpret_cast<const uint32_t*>(rec + code_off + 128u);
+          const uint32_t sml = *reinterpret_cast<const uint32_t*>(rec + sm_off), smh = *reinterpret_cast<const uint32_t*>(rec + sm_off + 32u);
           // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
-          const uint32_t l0 = (wl & 0x000f000fu) | 0x64006400u, h0 = (wl & 0x00f000f0u) | 0x64006400u;
-          const uint32_t l1 = ((wl >> 8) & 0x000f000fu) | 0x64006400u, h1 = ((wl >> 8) & 0x00f000f0u) | 0x64006400u;
-          const uint32_t L0 = (wh & 0x000f000fu) | 0x64006400u, H0 = (wh & 0x00f000f0u) | 0x64006400u;
-          const uint32_t L1 = ((wh >> 8) & 0x000f000fu) | 0x64006400u, H1 = ((wh >> 8) & 0x00f000f0u) | 0x64006400u;
-          const float sl = __half2float(__ushort_as_half((unsigned short)(sml & 0xffffu))), ml = __half2float(__ushort_as_half((unsigned short)(sml >> 16)));
-          const float sh = __half2float(__ushort_as_half((unsigned short)(smh & 0xffffu))), mh = __half2float(__ushort_as_half((unsigned short)(smh >> 16)));
+          const uint32_t wl8 = wl >> 8, wh8 = wh >> 8;
+          const uint32_t l0 = and_or(wl, MLO, MAGIC), h0 = and_or(wl, MHI, MAGIC), l1 = and_or(wl8, MLO, MAGIC), h1 = and_or(wl8, MHI, MAGIC);
+          const uint32_t L0 = and_or(wh, MLO, MAGIC), H0 = and_or(wh, MHI, MAGIC), L1 = and_or(wh8, MLO, MAGIC), H1 = and_or(wh8, MHI, MAGIC);
+          const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&sml)), fh = __half22float2(*reinterpret_cast<const __half2*>(&smh));   // (scale, min)
 #pragma unroll
           for (int h = 0; h < MP / 8; h++) {
             // token columns past M hold zeros; their lanes skip the load (no row of the token tile exists for them)
             uint4 b = make_uint4(0, 0, 0, 0);
-            if (g + 8 * h < p.M) b = *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8 * h) * tok_stride + gi * 64u + t4 * 16u);
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            mma_16816(acc, l0, L0, h0, H0, b.x, b.y);
-            mma_16816(acc, l1, L1, h1, H1, b.z, b.w);
-            const uint32_t ta = min(2u * t4 + 8u * h, p.M - 1u), tb = min(2u * t4 + 1u + 8u * h, p.M - 1u);
-            const float2 c0 = cs[ta * csld + gi], c1 = cs[tb * csld + gi];
-            tot[h][0] = fmaf(ml, c0.y, fmaf(sl, acc[0] - c0.x, tot[h][0]));
-            tot[h][1] = fmaf(ml, c1.y, fmaf(sl, acc[1] - c1.x, tot[h][1]));
-            tot[h][2] = fmaf(mh, c0.y, fmaf(sh, acc[2] - c0.x, tot[h][2]));
-            tot[h][3] = fmaf(mh, c1.y, fmaf(sh, acc[3] - c1.x, tot[h][3]));
+            if (h == 0 ? tok0 : tok1) b = *reinterpret_cast<const uint4*>((h == 0 ? xk0 : xk1) + r * 64u);
+            const float4 c = *reinterpret_cast<const float4*>(ck + (r * (MP / 2) + 4 * h) * 4u);      // (-C_a, Sx_a, -C_b, Sx_b)
+            const float cin[4] = {c.x, c.z, c.x, c.z};
+            float acc[4], acc2[4];
+            mma_16816(acc, l0, L0, h0, H0, b.x, b.y, cin);
+            mma_16816(acc2, l1, L1, h1, H1, b.z, b.w, acc);
+            tot[h][0] = fmaf(fl.y, c.y, fmaf(fl.x, acc2[0], tot[h][0]));
+            tot[h][1] = fmaf(fl.y, c.w, fmaf(fl.x, acc2[1], tot[h][1]));
+            tot[h][2] = fmaf(fh.y, c.y, fmaf(fh.x, acc2[2], tot[h][2]));
+            tot[h][3] = fmaf(fh.y, c.w, fmaf(fh.x, acc2[3], tot[h][3]));
           }
         }
       } else {
 #pragma unroll
         for (uint32_t r = 0; r < D_STAGE_K / 64u; r++) {
-          if (r * 64u >= kk) break;
           const unsigned char* rec = st + r * 4224u;
-          const uint32_t gi = (k >> 5) + 2u * r;          // first of the record's two 32-k token groups
-          const uint4 ql = *reinterpret_cast<const uint4*>(rec + rlo * 64u + t4 * 16u), qh = *reinterpret_cast<const uint4*>(rec + rhi * 64u + t4 * 16u);
-          const float sl = __half2float(*reinterpret_cast<const __half*>(rec + 4096u + rlo * 2u)), sh = __half2float(*reinterpret_cast<const __half*>(rec + 4096u + rhi * 2u));
+          const uint4 ql = *reinterpret_cast<const uint4*>(rec + code_off), qh = *reinterpret_cast<const uint4*>(rec + code_off + 512u);
+          const float sl = __half2float(*reinterpret_cast<const __half*>(rec + sm_off)), sh = __half2float(*reinterpret_cast<const __half*>(rec + sm_off + 16u));
           const uint32_t wl[4] = {ql.x ^ 0x80808080u, ql.y ^ 0x80808080u, ql.z ^ 0x80808080u, ql.w ^ 0x80808080u};
           const uint32_t wh[4] = {qh.x ^ 0x80808080u, qh.y ^ 0x80808080u, qh.z ^ 0x80808080u, qh.w ^ 0x80808080u};
 #pragma unroll
           for (int h = 0; h < MP / 8; h++) {
             // this lane's 16 columns of the record: 16*t4 .. 16*t4+15, natural order, 32 bytes
-            const unsigned char* bp = xs + (size_t)(g + 8 * h) * tok_stride + gi * 64u + t4 * 32u;
+            const unsigned char* bp = (h == 0 ? xk0 : xk1) + r * 128u;
             uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-            if (g + 8 * h < p.M) { b0 = *reinterpret_cast<const uint4*>(bp); b1 = *reinterpret_cast<const uint4*>(bp + 16); }
+            if (h == 0 ? tok0 : tok1) { b0 = *reinterpret_cast<const uint4*>(bp); b1 = *reinterpret_cast<const uint4*>(bp + 16); }
             const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float2 c = *reinterpret_cast<const float2*>(ck + (r * (MP / 2) + 4 * h) * 2u);      // (-C_a, -C_b)
+            float acc[4] = {c.x, c.y, c.x, c.y};
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-              mma_16816(acc, __byte_perm(wl[j], 0x64646464u, 0x4140), __byte_perm(wh[j], 0x64646464u, 0x4140),
-                        __byte_perm(wl[j], 0x64646464u, 0x4342), __byte_perm(wh[j], 0x64646464u, 0x4342), bb[2 * j], bb[2 * j + 1]);
-            const uint32_t ta = min(2u * t4 + 8u * h, p.M - 1u), tb = min(2u * t4 + 1u + 8u * h, p.M - 1u);
-            const float2 a0 = cs[ta * csld + gi], a1 = cs[ta * csld + gi + 1];
-            const float2 e0 = cs[tb * csld + gi], e1 = cs[tb * csld + gi + 1];
-            const float C0 = a0.x + a1.x, C1 = e0.x + e1.x;
-            tot[h][0] = fmaf(sl, acc[0] - C0, tot[h][0]);
-            tot[h][1] = fmaf(sl, acc[1] - C1, tot[h][1]);
-            tot[h][2] = fmaf(sh, acc[2] - C0, tot[h][2]);
-            tot[h][3] = fmaf(sh, acc[3] - C1, tot[h][3]);
+            for (int j = 0; j < 4; j++) {
+              float nx[4];
+              mma_16816(nx, __byte_perm(wl[j], 0x64646464u, 0x4140), __byte_perm(wh[j], 0x64646464u, 0x4140),
+                        __byte_perm(wl[j], 0x64646464u, 0x4342), __byte_perm(wh[j], 0x64646464u, 0x4342), bb[2 * j], bb[2 * j + 1], acc);
+#pragma unroll
+              for (int i = 0; i < 4; i++) acc[i] = nx[i];
+            }
+            tot[h][0] = fmaf(sl, acc[0], tot[h][0]);
+            tot[h][1] = fmaf(sl, acc[1], tot[h][1]);
+            tot[h][2] = fmaf(sh, acc[2], tot[h][2]);
+            tot[h][3] = fmaf(sh, acc[3], tot[h][3]);
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8u * s);
+      if (++s == D_STAGES) { s = 0; ph ^= 1u; }
     }
     if (!ok) continue;
     // ---- this unit's partial sums: scratch[kb][token][slot]
@@ -264,7 +290,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     for (int h = 0; h < MP / 8; h++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rhi : rlo;
+        const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rlo + 8u : rlo;
         if (tok < p.M) d.scratch[((size_t)kb * p.M + tok) * d.nslots + t * 64u + row] = tot[h][i];
       }
     }
@@ -305,14 +331,17 @@ inline bool decode_supported(const KP& p) {
 
 template <int ENC, int XMODE>
 inline cudaError_t launch_decode_t(const DecodeP& d, int grid, size_t smem, cudaStream_t st) {
-  cudaError_t e;
-  if (d.Mp == 8) {
-    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    k_decode_stream<ENC, XMODE, 8><<<grid, D_THREADS, smem, st>>>(d);
-  } else {
-    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    k_decode_stream<ENC, XMODE, 16><<<grid, D_THREADS, smem, st>>>(d);
+  // the dynamic shared memory ceiling of each instantiation is raised once (D_SMEM_MAX covers every configuration)
+  static bool ready = false;
+  if (!ready) {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_MAX)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_MAX)) != cudaSuccess) return e;
+    ready = true;
   }
+  if (smem > (size_t)D_SMEM_MAX) return cudaErrorInvalidValue;
+  if (d.Mp == 8) k_decode_stream<ENC, XMODE, 8><<<grid, D_THREADS, smem, st>>>(d);
+  else k_decode_stream<ENC, XMODE, 16><<<grid, D_THREADS, smem, st>>>(d);
   return cudaGetLastError();
 }
 
@@ -338,8 +367,9 @@ inline int launch_decode(p0p_ctx* c, const KP& p) {
   if (int r = ensure_scratch(c, sbytes + 256)) return r;
   d.scratch = reinterpret_cast<float*>(c->scratch);
   d.status = c->dev_status;
-  const uint32_t tok_stride = (d.KC / 32u) * 64u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
-  const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES + ((p.M * tok_stride + 127u) & ~127u) + (((size_t)p.M * (d.KC / 32u) * 8u + 15u) & ~15u) + 2u * D_STAGES * 8u + 128u;
+  const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
+  const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 16u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 8u;
+  const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES + ((p.M * tok_stride + 127u) & ~127u) + ct_bytes + 2u * D_STAGES * 8u + 128u;
   const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (size_t)(c->prop.sharedMemPerMultiprocessor) / (smem + 1024)));
   const int grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * sms);      // every block is resident: the unit ranges run side by side
   cudaError_t e;

@@ -241,11 +241,51 @@ int p0p_host_free(p0p_ctx* c, void* p) {
   return 0;
 }
 
+struct p0p_graph { cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr; };
+
+int p0p_capture_begin(p0p_ctx* c) {
+  P0P_ALIVE(c);
+  if (c->capturing) return fail(c, -1, "capture: already recording");
+  DeviceGuard g(c->device);
+  P0P_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "capture begin");
+  c->capturing = true;
+  return 0;
+}
+int p0p_capture_end(p0p_ctx* c, p0p_graph** out) {
+  if (!c || !out) return -1;
+  if (!c->capturing) return fail(c, -1, "capture: not recording");
+  DeviceGuard g(c->device);
+  c->capturing = false;
+  p0p_graph* gr = new p0p_graph();
+  cudaError_t e = cudaStreamEndCapture(c->stream, &gr->graph);
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&gr->exec, gr->graph, 0);
+  if (e != cudaSuccess) { if (gr->graph) cudaGraphDestroy(gr->graph); delete gr; return cuda_fail(c, e, "capture end"); }
+  *out = gr;
+  return 0;
+}
+int p0p_graph_launch(p0p_ctx* c, p0p_graph* gr) {
+  P0P_ALIVE(c);
+  if (!gr || !gr->exec) return fail(c, -1, "graph: null graph");
+  DeviceGuard g(c->device);
+  P0P_CUDA(c, cudaGraphLaunch(gr->exec, c->stream), "graph launch");
+  return 0;
+}
+int p0p_graph_free(p0p_ctx* c, p0p_graph* gr) {
+  if (!c) return -1;
+  if (!gr) return 0;
+  DeviceGuard g(c->device);
+  if (gr->exec) cudaGraphExecDestroy(gr->exec);
+  if (gr->graph) cudaGraphDestroy(gr->graph);
+  delete gr;
+  return 0;
+}
+
 }  // extern "C"
 
 namespace p0p {
 int ensure_scratch(p0p_ctx* c, uint64_t bytes) {
   if (c->scratch_bytes >= bytes) return 0;
+  if (c->capturing) return fail(c, -11, "this call needs %llu bytes of scratch memory, which cannot be sized while recording: run it once before p0p_capture_begin", (unsigned long long)bytes);
   if (c->scratch) { cudaStreamSynchronize(c->stream); cudaFree(c->scratch); c->scratch = nullptr; c->scratch_bytes = 0; }
   uint64_t want = bytes < (8ull << 20) ? (8ull << 20) : (bytes + (1ull << 20) - 1) & ~((1ull << 20) - 1);
   cudaError_t e = cudaMalloc(&c->scratch, want);

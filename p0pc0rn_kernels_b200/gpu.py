@@ -194,6 +194,19 @@ class Gpu:
     def cap(self, kind="mm"):
         return self.rate[kind] * self.opts["maxDispatchSeconds"]
 
+    # ---------------------------------------------------------------- recorded launch sequences (the Runner's batching, src/core/gpu.js:203-257)
+    def record(self, fn) -> "Graph":
+        """Run fn() with every op call recorded instead of executed; returns a Graph whose launch() replays them.
+        Call fn() once normally first (the first call of a shape sizes the library's scratch memory)."""
+        self._check(lib.p0p_capture_begin(self._h))
+        try:
+            fn()
+        finally:
+            h = C.c_void_p()
+            rc = lib.p0p_capture_end(self._h, C.byref(h))
+        self._check(rc)
+        return Graph(self, h)
+
     # ---------------------------------------------------------------- extras the CUDA build adds
     @property
     def stream(self) -> int:
@@ -212,6 +225,20 @@ class Gpu:
             lib.p0p_close(self._h)
             self._h = C.c_void_p()
             self.bufs.clear()
+
+
+class Graph:
+    """a recorded sequence of op calls"""
+
+    def __init__(self, gpu, handle):
+        self._g, self._h = gpu, handle
+
+    def launch(self):
+        self._g._check(lib.p0p_graph_launch(self._g._h, self._h))
+
+    def free(self):
+        if self._h:
+            lib.p0p_graph_free(self._g._h, self._h); self._h = None
 
 
 def createGpu(opts=None) -> Gpu:

@@ -298,6 +298,25 @@ def test_dequant_bit_exact(gpu, oracle, enc, scale, path):
         gpu.free(wb); gpu.free(ob)
 
 
+def test_recorded_sequence(gpu, oracle):
+    """op calls recorded into a graph (the Runner's batching, src/core/gpu.js:203-257) replay to the same bits"""
+    h = CS.build(dict(enc="q4", M=4, N=256, K=512, xmode="rms", epi="swiglu"))
+    want = CS.run_gpu(gpu, h)
+    bufs = {k: gpu.upload(h[k], k) for k in ("X", "W", "ST", "PV")}
+    bufs["Y"] = gpu.upload(h["Y0"], "Y")
+    try:
+        a = CS.gemm_args(gpu, h, bufs)
+        P().gemm(gpu, a)                                  # first call sizes scratch memory
+        gpu.upload(h["Y0"], "", bufs["Y"], 0)
+        g = gpu.record(lambda: P().gemm(gpu, a))
+        assert np.array_equal(gpu.read(bufs["Y"]).view(np.uint16)[: h["Y0"].size], h["Y0"]), "recording must not run the op"
+        g.launch(); g.launch()
+        assert np.array_equal(gpu.read(bufs["Y"]).view(np.uint16)[: h["Y0"].size], want)
+        g.free()
+    finally:
+        for b in bufs.values(): gpu.free(b)
+
+
 def test_rowstats(gpu, oracle):
     O = oracle
     rows, cols = 37, 1000
