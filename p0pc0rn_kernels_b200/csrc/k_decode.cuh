@@ -26,13 +26,13 @@
 
 namespace p0p {
 
-constexpr int D_CONSUMERS = 128;            // 4 warps x 16 rows
+constexpr int D_CONSUMERS = 256;            // 8 warps: 4 row groups of 16 rows x 2 warps that split each stage's records
 constexpr int D_THREADS = D_CONSUMERS + 32; // + the producer warp
-constexpr int D_STAGES = 6;
-constexpr int D_STAGE_K = 128;              // k per stage: 4 q4 records (5120 B) or 2 q8 records (8448 B)
-constexpr int D_STAGE_BYTES = 8448;
-constexpr int D_MAX_KC = 4096;              // largest k-block
-constexpr int D_SMEM_MAX = 112 * 1024;      // dynamic shared memory ceiling of the stream kernel
+constexpr int D_STAGES = 5;
+constexpr int D_STAGE_K = 256;              // k per stage: 8 q4 records (10240 B) or 4 q8 records (16896 B): one bulk copy each
+constexpr int D_STAGE_BYTES_Q4 = 10240, D_STAGE_BYTES_Q8 = 16896;
+constexpr int D_MAX_KC = 2048;              // largest k-block
+constexpr int D_SMEM_MAX = 144 * 1024;      // dynamic shared memory ceiling of the stream kernel
 
 struct DecodeP {
   KP p;
@@ -44,6 +44,7 @@ struct DecodeP {
   uint32_t nslots;    // tiles * 64
   float* scratch;     // [S][M][nslots] fp32
   int* status;
+  int dbg_skip;
 };
 
 // weight tile index (64 rows) of unit-local tile t
@@ -54,10 +55,11 @@ __device__ __forceinline__ uint32_t d_tile_row0(const DecodeP& d, uint32_t t) {
 
 // ---- token staging: one thread per (token, scale group: 32 k for q4, 64 k for q8).  Writes the group's tokens in
 // operand order and its correction terms.
-//   q4: ct[gi][token pair] = float4(-C_a, Sx_a, -C_b, Sx_b),  C = 1024 * sum(x, even k) + 64 * sum(x, odd k)
-//   q8: ct[gi][token pair] = float2(-C_a, -C_b),              C = 1152 * sum(x)
+//   ctc[gi][token pair] = float4(-C_a, -C_b, -C_a, -C_b): the accumulator fragment (rows g / g+8 x tokens a, b) the
+//                         multiply starts from;  q4: C = 1024 * sum(x, even k) + 64 * sum(x, odd k),  q8: C = 1152 * sum(x)
+//   cts[gi][token pair] = float2(Sx_a, Sx_b), the plain sums (q4 only: they carry the group minimum)
 template <int ENC, int XMODE, int MP>
-__device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float* ct, uint32_t tok_stride, uint32_t tid) {
+__device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float* ctc, float* cts, uint32_t tok_stride, uint32_t tid) {
   const KP& p = d.p;
   constexpr uint32_t GS = ENC == P0P_ENC_Q4 ? 32u : 64u;
   const uint32_t groups = klen / GS;
@@ -114,15 +116,24 @@ __device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, u
 #pragma unroll
       for (int q = 0; q < 4; q++) dst[q] = reinterpret_cast<const uint4*>(o)[q];
     }
-    if (ENC == P0P_ENC_Q4) {
-      // even nibbles enter the multiply as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q
-      float* c = ct + ((size_t)gi * (MP / 2) + (m >> 1)) * 4u + (m & 1u) * 2u;
-      c[0] = -(1024.0f * se + 64.0f * (sx - se)); c[1] = sx;
-    } else {
-      ct[((size_t)gi * (MP / 2) + (m >> 1)) * 2u + (m & 1u)] = -1152.0f * sx;        // codes enter as 1024 + 128 + q
-    }
+    // q4: even nibbles enter the multiply as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q;  q8: codes enter as 1024 + 128 + q
+    const float negc = ENC == P0P_ENC_Q4 ? -(1024.0f * se + 64.0f * (sx - se)) : -1152.0f * sx;
+    float* c = ctc + ((size_t)gi * (MP / 2) + (m >> 1)) * 4u + (m & 1u);
+    c[0] = negc; c[2] = negc;
+    if (ENC == P0P_ENC_Q4) cts[((size_t)gi * (MP / 2) + (m >> 1)) * 2u + (m & 1u)] = sx;
   }
 }
+
+// Loads through 32-bit shared-window addresses: address arithmetic stays in 32 bits and folds into immediates.
+// They are plain (non-volatile) asm so that the compiler may overlap the records of a stage; `anchor` ties their
+// addresses to a point after the stage's mbarrier wait, so none of them can move above it.
+__device__ __forceinline__ uint32_t anchor(uint32_t a) { uint32_t v; asm volatile("mov.u32 %0, %1;" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint16_t lds16(uint32_t a) { uint16_t v; asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds64(uint32_t a) { uint2 v; asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds128(uint32_t a) { uint4 v; asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
+__device__ __forceinline__ float2 lds64f(uint32_t a) { float2 v; asm("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ float4 lds128f(uint32_t a) { float4 v; asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v; }
 
 // (a & mask) | magic in ONE instruction (left to the compiler this becomes two)
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t magic) {
@@ -133,7 +144,7 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t m
 
 // D = A * B + C with C given separately (the correction terms ride in on C)
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, const float (&c)[4]) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
@@ -144,27 +155,32 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   const KP& p = d.p;
   constexpr uint32_t TOK_PAD = ENC == P0P_ENC_Q4 ? 64u : 16u;           // keeps the operand loads free of bank conflicts
   constexpr uint32_t GS = ENC == P0P_ENC_Q4 ? 32u : 64u;
-  constexpr uint32_t CT_F = ENC == P0P_ENC_Q4 ? 4u : 2u;                // floats per (group, token pair) in the correction table
   const uint32_t tok_stride = d.KC * 2u + TOK_PAD;
-  // layout: stages | token tile | correction table | barriers
+  // layout: stages | token tile (M rows + one row of zeros) | C fragments | Sx pairs | pair-combine buffer | barriers
   unsigned char* stages = smem;
+  constexpr uint32_t D_STAGE_BYTES = ENC == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8;
   unsigned char* xs = stages + D_STAGES * D_STAGE_BYTES;
-  float* ct = reinterpret_cast<float*>(xs + ((p.M * tok_stride + 127u) & ~127u));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ct) + (d.KC / GS) * (MP / 2) * CT_F * 4u);
+  float* ctc = reinterpret_cast<float*>(xs + (((p.M + 1u) * tok_stride + 127u) & ~127u));       // [group][pair] float4 (-Ca, -Cb, -Ca, -Cb)
+  float* cts = ctc + (d.KC / GS) * (MP / 2) * 4u;                                              // [group][pair] float2 (Sx_a, Sx_b)   (q4 only)
+  float* comb = cts + (ENC == P0P_ENC_Q4 ? (d.KC / GS) * (MP / 2) * 2u : 0u);                  // [4 row groups][32 lanes][MP/2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(comb + 4u * 32u * (MP / 2));
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + D_STAGES);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   if (tid == 0) {
-    for (int s = 0; s < D_STAGES; s++) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 4); }
+    for (int s = 0; s < D_STAGES; s++) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, D_CONSUMERS / 32); }
     fence_mbar_init();
   }
+  // the row of zeros that token columns past M read
+  for (uint32_t i = tid; i < tok_stride / 16u; i += D_THREADS) reinterpret_cast<uint4*>(xs + (size_t)p.M * tok_stride)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
 
   const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * d.units) / gridDim.x), u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * d.units) / gridDim.x);
   constexpr uint32_t REC = ENC == P0P_ENC_Q4 ? 1280u : 4224u, REC_K = ENC == P0P_ENC_Q4 ? 32u : 64u;
   constexpr uint32_t STAGE_TX = (D_STAGE_K / REC_K) * REC;              // a k-block is a whole number of stages (K % 128 == 0)
+  constexpr uint32_t RPW = (D_STAGE_K / REC_K) / 2u;                    // records of a stage per consumer warp (two warps share 16 rows)
 
-  if (warp == 4) {
+  if (warp == D_CONSUMERS / 32) {
     // ------------------------------------------------------------------ producer: one lane streams the records
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
@@ -184,18 +200,21 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     return;
   }
 
-  // -------------------------------------------------------------------- consumers
-  const uint32_t g = lane >> 2, t4 = lane & 3u;
-  const uint32_t rlo = warp * 16u + g;                                   // this lane's rows: rlo and rlo + 8
-  // byte offsets that stay fixed for the whole kernel
-  const uint32_t code_off = ENC == P0P_ENC_Q4 ? rlo * 16u + t4 * 4u : rlo * 64u + t4 * 16u;
-  const uint32_t sm_off = ENC == P0P_ENC_Q4 ? 1024u + rlo * 4u : 4096u + rlo * 2u;
-  const bool tok0 = g < p.M, tok1 = g + 8u < p.M;                        // does this lane's token column exist?
-  const unsigned char* xrow0 = xs + (size_t)g * tok_stride + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
-  const unsigned char* xrow1 = xrow0 + 8u * (size_t)tok_stride;
-  const float* ctl = ct + t4 * CT_F;                                     // this lane's token pair (2 t4, 2 t4 + 1); + 4 pairs for tokens 8..15
-  uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
+  // -------------------------------------------------------------------- consumers: warp = (half, row group)
+  const uint32_t g = lane >> 2, t4 = lane & 3u, rg = warp & 3u, half = warp >> 2;
+  const uint32_t rlo = rg * 16u + g;                                     // this lane's rows: rlo and rlo + 8
+  // shared-window addresses that stay fixed for the whole kernel (this warp's first record of a stage included)
+  const uint32_t code0 = smem_u32(stages) + half * RPW * REC + (ENC == P0P_ENC_Q4 ? rlo * 16u + t4 * 4u : rlo * 64u + t4 * 16u);
+  const uint32_t sm0 = smem_u32(stages) + half * RPW * REC + (ENC == P0P_ENC_Q4 ? 1024u + rlo * 4u : 4096u + rlo * 2u);
+  // token columns past M read the row of zeros
+  const uint32_t xrow0 = smem_u32(xs) + min(g, p.M) * tok_stride + half * RPW * REC_K * 2u + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
+  const uint32_t xrow1 = smem_u32(xs) + min(g + 8u, p.M) * tok_stride + half * RPW * REC_K * 2u + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
+  const uint32_t ctc_l = smem_u32(ctc) + (half * RPW * (MP / 2) + t4) * 16u;   // this lane's token pair (2 t4, 2 t4 + 1); + 4 pairs for tokens 8..15
+  const uint32_t cts_l = smem_u32(cts) + (half * RPW * (MP / 2) + t4) * 8u;
+  float* comb_l = comb + (rg * 32u + lane) * (MP / 2);
   const uint32_t MLO = 0x000f000fu, MHI = 0x00f000f0u, MAGIC = 0x64006400u;
+  const bool one = p.M == 1u;                                            // a single token: only the accumulators of token 0 are kept up
+  uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
   bool ok = true;
   // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
   // the named barriers below, so nobody is left waiting for it.
@@ -204,29 +223,29 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
     if (kb != cur_kb) {                       // a new k-block: restage the tokens (all consumers are past the old ones)
       bar_sync_named(1, D_CONSUMERS);
-      if (ok) d_stage_tokens<ENC, XMODE, MP>(d, k_beg, klen, xs, ct, tok_stride, tid);
+      if (ok) d_stage_tokens<ENC, XMODE, MP>(d, k_beg, klen, xs, ctc, cts, tok_stride, tid);
       bar_sync_named(1, D_CONSUMERS);
       cur_kb = kb;
     }
-    if (!ok) continue;
     float tot[MP / 8][4];
 #pragma unroll
     for (int h = 0; h < MP / 8; h++)
 #pragma unroll
       for (int i = 0; i < 4; i++) tot[h][i] = 0.0f;
 
-    for (uint32_t k = 0; k < klen; k += D_STAGE_K) {
+    for (uint32_t k = 0; ok && k < klen; k += D_STAGE_K) {
       if (!mbar_wait(full0 + 8u * s, ph, d.status, 102)) { ok = false; break; }
-      const unsigned char* st = stages + s * D_STAGE_BYTES;
-      const unsigned char* xk0 = xrow0 + k * 2u;
-      const unsigned char* xk1 = xrow1 + k * 2u;
-      const float* ck = ctl + (k / GS) * (MP / 2) * CT_F;
+      const uint32_t so = anchor(s * D_STAGE_BYTES), ko = anchor(k);
+      const uint32_t ca = code0 + so, sa = sm0 + so;
+      const uint32_t xk0 = xrow0 + ko * 2u, xk1 = xrow1 + ko * 2u;
+      const uint32_t ck = ctc_l + (ko / GS) * (MP / 2) * 16u;
+      if (d.dbg_skip) { tot[0][0] += __uint_as_float(lds32(ca)); } else
       if (ENC == P0P_ENC_Q4) {
+        const uint32_t sk = cts_l + (ko / GS) * (MP / 2) * 8u;
 #pragma unroll
-        for (uint32_t r = 0; r < D_STAGE_K / 32u; r++) {
-          const unsigned char* rec = st + r * 1280u;
-          const uint32_t wl = *reinterpret_cast<const uint32_t*>(rec + code_off), wh = *reinterpret_cast<const uint32_t*>(rec + code_off + 128u);
-          const uint32_t sml = *reinterpret_cast<const uint32_t*>(rec + sm_off), smh = *reinterpret_cast<const uint32_t*>(rec + sm_off + 32u);
+        for (uint32_t r = 0; r < RPW; r++) {
+          const uint32_t wl = lds32(ca + r * 1280u), wh = lds32(ca + r * 1280u + 128u);
+          const uint32_t sml = lds32(sa + r * 1280u), smh = lds32(sa + r * 1280u + 32u);
           // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
           const uint32_t wl8 = wl >> 8, wh8 = wh >> 8;
           const uint32_t l0 = and_or(wl, MLO, MAGIC), h0 = and_or(wl, MHI, MAGIC), l1 = and_or(wl8, MLO, MAGIC), h1 = and_or(wl8, MHI, MAGIC);
@@ -234,37 +253,36 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
           const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&sml)), fh = __half22float2(*reinterpret_cast<const __half2*>(&smh));   // (scale, min)
 #pragma unroll
           for (int h = 0; h < MP / 8; h++) {
-            // token columns past M hold zeros; their lanes skip the load (no row of the token tile exists for them)
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (h == 0 ? tok0 : tok1) b = *reinterpret_cast<const uint4*>((h == 0 ? xk0 : xk1) + r * 64u);
-            const float4 c = *reinterpret_cast<const float4*>(ck + (r * (MP / 2) + 4 * h) * 4u);      // (-C_a, Sx_a, -C_b, Sx_b)
-            const float cin[4] = {c.x, c.z, c.x, c.z};
+            const uint4 b = lds128((h == 0 ? xk0 : xk1) + r * 64u);
+            const float4 c = lds128f(ck + (r * (MP / 2) + 4 * h) * 16u);      // the accumulator starts at -C
+            const float2 sx = lds64f(sk + (r * (MP / 2) + 4 * h) * 8u);
+            const float cin[4] = {c.x, c.y, c.z, c.w};
             float acc[4], acc2[4];
             mma_16816(acc, l0, L0, h0, H0, b.x, b.y, cin);
             mma_16816(acc2, l1, L1, h1, H1, b.z, b.w, acc);
-            tot[h][0] = fmaf(fl.y, c.y, fmaf(fl.x, acc2[0], tot[h][0]));
-            tot[h][1] = fmaf(fl.y, c.w, fmaf(fl.x, acc2[1], tot[h][1]));
-            tot[h][2] = fmaf(fh.y, c.y, fmaf(fh.x, acc2[2], tot[h][2]));
-            tot[h][3] = fmaf(fh.y, c.w, fmaf(fh.x, acc2[3], tot[h][3]));
+            tot[h][0] = fmaf(fl.y, sx.x, fmaf(fl.x, acc2[0], tot[h][0]));
+            tot[h][2] = fmaf(fh.y, sx.x, fmaf(fh.x, acc2[2], tot[h][2]));
+            if (!one) {
+              tot[h][1] = fmaf(fl.y, sx.y, fmaf(fl.x, acc2[1], tot[h][1]));
+              tot[h][3] = fmaf(fh.y, sx.y, fmaf(fh.x, acc2[3], tot[h][3]));
+            }
           }
         }
       } else {
 #pragma unroll
-        for (uint32_t r = 0; r < D_STAGE_K / 64u; r++) {
-          const unsigned char* rec = st + r * 4224u;
-          const uint4 ql = *reinterpret_cast<const uint4*>(rec + code_off), qh = *reinterpret_cast<const uint4*>(rec + code_off + 512u);
-          const float sl = __half2float(*reinterpret_cast<const __half*>(rec + sm_off)), sh = __half2float(*reinterpret_cast<const __half*>(rec + sm_off + 16u));
+        for (uint32_t r = 0; r < RPW; r++) {
+          const uint4 ql = lds128(ca + r * 4224u), qh = lds128(ca + r * 4224u + 512u);
+          const float sl = __half2float(__ushort_as_half(lds16(sa + r * 4224u))), sh = __half2float(__ushort_as_half(lds16(sa + r * 4224u + 16u)));
           const uint32_t wl[4] = {ql.x ^ 0x80808080u, ql.y ^ 0x80808080u, ql.z ^ 0x80808080u, ql.w ^ 0x80808080u};
           const uint32_t wh[4] = {qh.x ^ 0x80808080u, qh.y ^ 0x80808080u, qh.z ^ 0x80808080u, qh.w ^ 0x80808080u};
 #pragma unroll
           for (int h = 0; h < MP / 8; h++) {
             // this lane's 16 columns of the record: 16*t4 .. 16*t4+15, natural order, 32 bytes
-            const unsigned char* bp = (h == 0 ? xk0 : xk1) + r * 128u;
-            uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-            if (h == 0 ? tok0 : tok1) { b0 = *reinterpret_cast<const uint4*>(bp); b1 = *reinterpret_cast<const uint4*>(bp + 16); }
+            const uint32_t bp = (h == 0 ? xk0 : xk1) + r * 128u;
+            const uint4 b0 = lds128(bp), b1 = lds128(bp + 16u);
             const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            const float2 c = *reinterpret_cast<const float2*>(ck + (r * (MP / 2) + 4 * h) * 2u);      // (-C_a, -C_b)
-            float acc[4] = {c.x, c.y, c.x, c.y};
+            const float4 c = lds128f(ck + (r * (MP / 2) + 4 * h) * 16u);      // the accumulator starts at -C
+            float acc[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
               float nx[4];
@@ -284,16 +302,26 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
       if (lane == 0) mbar_arrive(empty0 + 8u * s);
       if (++s == D_STAGES) { s = 0; ph ^= 1u; }
     }
-    if (!ok) continue;
-    // ---- this unit's partial sums: scratch[kb][token][slot]
+    // ---- the two warps of a row group add up (through shared memory), then this unit's partial sums go to
+    // scratch[kb][token][slot].  Both named barriers are met in drain mode too.
+    if (half == 1u) {
 #pragma unroll
-    for (int h = 0; h < MP / 8; h++) {
+      for (int h = 0; h < MP / 8; h++) *reinterpret_cast<float4*>(comb_l + 4 * h) = make_float4(tot[h][0], tot[h][1], tot[h][2], tot[h][3]);
+    }
+    bar_sync_named(2 + rg, 64);
+    if (half == 0u && ok) {
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rlo + 8u : rlo;
-        if (tok < p.M) d.scratch[((size_t)kb * p.M + tok) * d.nslots + t * 64u + row] = tot[h][i];
+      for (int h = 0; h < MP / 8; h++) {
+        const float4 o = *reinterpret_cast<const float4*>(comb_l + 4 * h);
+        const float v[4] = {tot[h][0] + o.x, tot[h][1] + o.y, tot[h][2] + o.z, tot[h][3] + o.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rlo + 8u : rlo;
+          if (tok < p.M) d.scratch[((size_t)kb * p.M + tok) * d.nslots + t * 64u + row] = v[i];
+        }
       }
     }
+    bar_sync_named(2 + rg, 64);
   }
 }
 
@@ -307,12 +335,21 @@ __global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
   if (p.epi == P0P_EPI_SWIGLU) slot = ((col & 1u) ? d.th * 64u : 0u) + (col >> 1);
   else slot = col;
   slot = min(slot, d.nslots - 1u);
+  // the partials of one output are read in batches of eight independent loads, then added in k-block order
   float acc[MP];
 #pragma unroll
-  for (int j = 0; j < MP; j++) {
-    float a = 0.0f;
-    if ((uint32_t)j < p.M) for (uint32_t kb = 0; kb < d.S; kb++) a += d.scratch[((size_t)kb * p.M + j) * d.nslots + slot];
-    acc[j] = a;
+  for (int j = 0; j < MP; j++) acc[j] = 0.0f;
+  for (uint32_t kb0 = 0; kb0 < d.S; kb0 += 8u) {
+#pragma unroll
+    for (int j = 0; j < MP; j++) {
+      if ((uint32_t)j < p.M) {
+        float v[8];
+#pragma unroll
+        for (uint32_t i = 0; i < 8u; i++) v[i] = kb0 + i < d.S ? __ldcg(d.scratch + ((size_t)(kb0 + i) * p.M + j) * d.nslots + slot) : 0.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < 8u; i++) acc[j] += v[i];
+      }
+    }
   }
   epilogue_cols<MP>(p, 0u, nB, c, acc, sh, 1);
 }
@@ -323,7 +360,7 @@ inline bool decode_supported(const KP& p) {
   if (p.xmode != P0P_X_F16 && p.xmode != P0P_X_LNMOD && p.xmode != P0P_X_RMS) return false;
   if (p.wR0 % 64u) return false;
   if (p.epi == P0P_EPI_SWIGLU && (p.wR1 % 64u)) return false;
-  if (p.K % 128u) return false;                       // a stage is 128 k
+  if (p.K % D_STAGE_K) return false;                  // k-blocks are whole stages
   if ((uintptr_t)p.W & 15u) return false;             // bulk copies need 16-byte aligned sources
   if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
   return true;
@@ -358,7 +395,7 @@ inline int launch_decode(p0p_ctx* c, const KP& p) {
   d.nslots = d.tiles * 64u;
   // k-block: as long as the token tile allows (about 32 KB), short enough for ~4 units per SM
   const uint32_t sms = (uint32_t)c->prop.multiProcessorCount;
-  uint32_t kc = p.M <= 4u ? 4096u : p.M <= 8u ? 2048u : 1024u;            // token tile of M * kc fp16 stays within 32 KB
+  uint32_t kc = p.M <= 8u ? 2048u : 1024u;                                // token tile of (M + 1) * kc fp16 stays near 32 KB
   const uint64_t want_units = 4ull * sms;
   while (kc > 256u && (uint64_t)d.tiles * ((p.K + kc - 1u) / kc) < want_units) kc >>= 1;
   if (kc > p.K) kc = p.K;
@@ -367,9 +404,10 @@ inline int launch_decode(p0p_ctx* c, const KP& p) {
   if (int r = ensure_scratch(c, sbytes + 256)) return r;
   d.scratch = reinterpret_cast<float*>(c->scratch);
   d.status = c->dev_status;
+  { const char* e = getenv("P0P_DECODE_SKIP"); d.dbg_skip = e && e[0] == '1'; }
   const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
-  const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 16u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 8u;
-  const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES + ((p.M * tok_stride + 127u) & ~127u) + ct_bytes + 2u * D_STAGES * 8u + 128u;
+  const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 16u;
+  const size_t smem = (size_t)D_STAGES * (p.enc == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8) + (((p.M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
   const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (size_t)(c->prop.sharedMemPerMultiprocessor) / (smem + 1024)));
   const int grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * sms);      // every block is resident: the unit ranges run side by side
   cudaError_t e;

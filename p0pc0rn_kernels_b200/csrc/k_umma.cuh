@@ -1,7 +1,338 @@
+// The tensor-core kernel for M > 16: tcgen05.mma with fp32 accumulators in tensor memory (TMEM).
+//
+// Orientation.  The 128 lanes of an accumulator are 128 weight rows (= output columns n) and its columns
+// are tokens:  D[n, m] = sum_k W[n, k] * X'[m, k].  Weights are the A operand (UMMA M = 128), tokens the B
+// operand (UMMA N = BT = 16..256 tokens), both K-major fp16 tiles of 64 k in shared memory with the 128-byte
+// swizzle.  A small M therefore costs a narrow instruction instead of a mostly empty 128-row tile, and every
+// epilogue thread owns one output column, which is what the fused epilogues need (epilogue.cuh).
+//
+// Pipeline of one block (persistent over output tiles, one block per SM), by warp:
+//   warp 0        producer   TMA tensor-map loads of the token tile (and of fp16 weights), bulk copies of the
+//                            quantised records (two 64-row record tiles x 64 k per step), all mbarrier-tracked
+//   warps 6..13   dequant    codes -> fp16 tile values f16(q*s+mn) / f16(q*s), bit-exact (packed HFMA2 path with a
+//                            per-warp exactness test and an fp32 fallback), written in the swizzled operand layout
+//   warp 1        MMA        one lane issues 4 x tcgen05.mma (k = 16 each) per step and commits to the stage's
+//                            "free" barrier; after the last step commits to the accumulator's "full" barrier
+//   warps 2..5    epilogue   tcgen05.ld of 16 tokens at a time, fused epilogue, global stores; two accumulators
+//                            (2 x 256 TMEM columns) let the next tile's multiply overlap
+// gate|up (swiglu) tiles interleave gate and up rows in the A tile, so that (gate, up) of one output sit in
+// adjacent lanes.  RMSNorm / LayerNorm+modulation prologues are applied by a one-pass kernel into an fp16
+// scratch copy of the tokens (the same token tile would otherwise be re-normalised by every column tile).
+// Every mbarrier wait is bounded (sync.cuh); on a time-out the block reports a code and winds down.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 #include "ctx.h"
+#include "epilogue.cuh"
+#include "sync.cuh"
+#include "umma.cuh"
+
 namespace p0p {
-inline bool umma_supported(const p0p_ctx*, const KP&) { return false; }
-inline int launch_umma(p0p_ctx*, const KP&) { return -9; }
+
+constexpr int U_THREADS = 448;           // 14 warps
+constexpr int U_NQ = 4;                  // stages of quantised records
+constexpr int U_A_BYTES = 128 * 128;     // one weight operand stage: 128 rows x 64 fp16
+constexpr int U_EPI_TB = 16;             // tokens per epilogue pass
+constexpr int U_TMEM_COLS = 512;
+
+struct UmmaP {
+  KP p;
+  uint32_t BT;          // tokens per tile (UMMA N): 16, 32, 64, 128 or 256
+  uint32_t NS;          // operand stages (3 or 4)
+  uint32_t n_tiles, m_tiles;
+  int* status;
+};
+
+template <int ENC> struct UQ { static constexpr uint32_t REC = 0, REC_K = 64, RB = 0, STAGE = 0; };
+template <> struct UQ<P0P_ENC_Q4> { static constexpr uint32_t REC = 1280, REC_K = 32, RB = 2560, STAGE = 5248; };   // 2 x (2 records) + 64 B pad between the record tiles
+template <> struct UQ<P0P_ENC_Q8> { static constexpr uint32_t REC = 4224, REC_K = 64, RB = 4224, STAGE = 8576; };
+
+__device__ __forceinline__ void sts128(uint32_t a, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
+__device__ __forceinline__ uint4 u_lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ uint32_t u_lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ uint16_t u_lds16(uint32_t a) { uint16_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory"); return v; }
+
+template <int ENC>
+__global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW) {
+  extern __shared__ unsigned char smem_raw[];
+  const KP& p = u.p;
+  const uint32_t BT = u.BT, NS = u.NS;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                     // operand tiles need 1024-byte alignment
+  unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t a_st = base, x_st = a_st + NS * U_A_BYTES, q_st = x_st + NS * BT * 128u;
+  const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : U_NQ * UQ<ENC>::STAGE);
+  const uint32_t bars = epi_sh + U_EPI_TB * 132u * 4u;
+  float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
+  // barrier slots (8 bytes each)
+  const uint32_t a_full = bars, x_full = a_full + 8u * 4u, ab_empty = x_full + 8u * 4u, wq_full = ab_empty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ;
+  const uint32_t acc_full = wq_empty + 8u * U_NQ, acc_empty = acc_full + 16u, tmem_slot = acc_empty + 16u;
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  if (tid == 0) {
+    for (uint32_t s = 0; s < 4u; s++) {
+      mbar_init(a_full + 8u * s, ENC == P0P_ENC_F16 ? 1u : 8u);
+      mbar_init(x_full + 8u * s, 1u);
+      mbar_init(ab_empty + 8u * s, 1u);
+    }
+    for (uint32_t s = 0; s < (uint32_t)U_NQ; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, 8u); }
+    for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, U_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gbase + (tmem_slot - base));
+
+  const uint32_t tiles = u.n_tiles * u.m_tiles, KS = p.K / 64u;
+  const bool swiglu = p.epi == P0P_EPI_SWIGLU;
+
+  if (warp == 0) {
+    // ================================================================= producer
+    if (lane == 0) {
+      uint32_t it = 0, itq = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles;
+        uint32_t trow[2];
+        if (ENC != P0P_ENC_F16) {
+          const uint32_t last = (p.Nw >> 6) - 1u;              // record tiles past the weight's end do not exist: their columns are never stored
+          if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
+          else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
+        }
+        for (uint32_t ks = 0; ks < KS; ks++, it++) {
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
+          if (!mbar_wait(ab_empty + 8u * s, ph ^ 1u, u.status, 201)) { ok = false; break; }
+          mbar_expect_tx(x_full + 8u * s, BT * 128u);
+          tma_load_2d(x_st + s * BT * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT), x_full + 8u * s);
+          if (ENC == P0P_ENC_F16) {
+            mbar_expect_tx(a_full + 8u * s, U_A_BYTES);
+            tma_load_2d(a_st + s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), a_full + 8u * s);
+          } else {
+            const uint32_t sq = itq % U_NQ, phq = (itq / U_NQ) & 1u;
+            if (!mbar_wait(wq_empty + 8u * sq, phq ^ 1u, u.status, 202)) { ok = false; break; }
+            mbar_expect_tx(wq_full + 8u * sq, 2u * UQ<ENC>::RB);
+            const size_t koff = (size_t)((p.wk0 + ks * 64u) / UQ<ENC>::REC_K) * UQ<ENC>::REC;
+            bulk_g2s(q_st + sq * UQ<ENC>::STAGE, p.W + (size_t)trow[0] * p.wG * UQ<ENC>::REC + koff, UQ<ENC>::RB, wq_full + 8u * sq);
+            bulk_g2s(q_st + sq * UQ<ENC>::STAGE + UQ<ENC>::RB + 64u, p.W + (size_t)trow[1] * p.wG * UQ<ENC>::REC + koff, UQ<ENC>::RB, wq_full + 8u * sq);
+            itq++;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================= MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(128u, BT);
+      uint32_t it = 0, tl = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, tl++) {
+        const uint32_t buf = tl & 1u;
+        if (!mbar_wait(acc_empty + 8u * buf, ((tl >> 1) & 1u) ^ 1u, u.status, 203)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256u;
+        for (uint32_t ks = 0; ks < KS; ks++, it++) {
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
+          if (!mbar_wait(a_full + 8u * s, ph, u.status, 204) || !mbar_wait(x_full + 8u * s, ph, u.status, 205)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t ad = umma_desc_sw128(a_st + s * U_A_BYTES), bd = umma_desc_sw128(x_st + s * BT * 128u);
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);   // +32 bytes (>>4) per 16 k
+          umma_commit(ab_empty + 8u * s);
+        }
+        if (ok) umma_commit(acc_full + 8u * buf);
+      }
+    }
+  } else if (warp < 6) {
+    // ================================================================= epilogue (TMEM lanes 32*(warp%4) .. +31)
+    const uint32_t q = warp & 3u, c = q * 32u + lane;
+    uint32_t tl = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, tl++) {
+      const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles, buf = tl & 1u;
+      if (ok && !mbar_wait(acc_full + 8u * buf, (tl >> 1) & 1u, u.status, 206)) ok = false;
+      tc_fence_after();
+      const uint32_t m0 = mt * BT, nchunks = min(BT, p.M - m0 + (U_EPI_TB - 1u)) / U_EPI_TB;
+      for (uint32_t ch = 0; ch < nchunks; ch++) {           // uniform over the four warps: the epilogue's named barrier needs all 128 threads
+        uint32_t r[16];
+        float acc[U_EPI_TB];
+        if (ok) { tmem_ld16(tmem_base + ((q * 32u) << 16) + buf * 256u + ch * U_EPI_TB, r); tmem_ld_wait(); }
+#pragma unroll
+        for (int j = 0; j < U_EPI_TB; j++) acc[j] = ok ? __uint_as_float(r[j]) : 0.0f;
+        epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+    }
+  } else if (ENC != P0P_ENC_F16) {
+    // ================================================================= dequantisation: codes -> swizzled fp16 operand rows
+    const uint32_t dw = warp - 6u;
+    uint32_t r, kh;                                        // this thread's operand row and which 32 k of the step
+    if (ENC == P0P_ENC_Q4) { r = (dw & 3u) * 32u + lane; kh = dw >> 2; }
+    else { r = dw * 16u + (lane >> 1); kh = lane & 1u; }
+    const uint32_t tsel = swiglu ? (r & 1u) : (r >> 6), rr = swiglu ? (r >> 1) : (r & 63u);
+    const uint32_t rsw = r & 7u, arow = r * 128u;
+    uint32_t it = 0, itq = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (uint32_t ks = 0; ks < KS; ks++, it++, itq++) {
+        const uint32_t sq = itq % U_NQ, phq = (itq / U_NQ) & 1u, s = it % NS, ph = (it / NS) & 1u;
+        if (!mbar_wait(wq_full + 8u * sq, phq, u.status, 207) || !mbar_wait(ab_empty + 8u * s, ph ^ 1u, u.status, 208)) { ok = false; break; }
+        const uint32_t rec = q_st + sq * UQ<ENC>::STAGE + tsel * (UQ<ENC>::RB + 64u);
+        const uint32_t dst = a_st + s * U_A_BYTES + arow;
+        __half2 v[16];
+        if (ENC == P0P_ENC_Q4) {
+          const uint4 cq = u_lds128(rec + kh * 1280u + rr * 16u);
+          const uint32_t sm = u_lds32(rec + kh * 1280u + 1024u + rr * 4u);
+          const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
+          if (__all_sync(0xffffffffu, q4_pair_exact(sm))) {
+            const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+#pragma unroll
+            for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
+          } else {
+            const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+          }
+        } else {
+          const uint32_t rot = (r >> 1) & 1u;                       // alternate the chunk order between row pairs: no bank conflicts
+          const uint32_t cb = rec + rr * 64u + kh * 32u;
+          const uint4 q0 = u_lds128(cb + rot * 16u), q1 = u_lds128(cb + (rot ^ 1u) * 16u);
+          const uint4 qa = rot ? q1 : q0, qb = rot ? q0 : q1;
+          const __half2 s2 = __half2half2(__ushort_as_half(u_lds16(rec + 4096u + rr * 2u)));
+          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+          for (int i = 0; i < 8; i++) q8_word_to_half2x2(w[i], s2, v + 2 * i);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) sts128(dst + (((kh * 4u + j) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[j]);
+        fence_proxy_async();                                        // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(a_full + 8u * s); mbar_arrive(wq_empty + 8u * sq); }
+      }
+    }
+  }
+  // ---- wind down: every role is past its last use of tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, U_TMEM_COLS); }
 }
+
+// ---- fused-norm prologue as one pass: X fp32 [M][ldx] -> X' fp16 [M][K] (src/ops/gemm.js:63-67)
+__global__ void k_prologue_f16(const KP p, __half* __restrict__ out) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4u;
+  if (i >= (size_t)p.M * p.K) return;
+  const uint32_t m = (uint32_t)(i / p.K), k = (uint32_t)(i % p.K);
+  const float4 x = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k));
+  const size_t sr = ((size_t)p.statOff + m) * 2u;
+  const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
+  const float* pv = p.PV + p.pvOff + p.kx0 + k;
+  const float xv[4] = {x.x, x.y, x.z, x.w};
+  __half o[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+    o[j] = __float2half_rn(p.xmode == P0P_X_LNMOD ? (xv[j] - mean) * rstd * (1.0f + __ldg(pv + j)) + __ldg(pv + p.pvStride + j) : xv[j] * rstd * __ldg(pv + j));
+  *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<const uint2*>(o);
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+typedef CUresult (*tmap_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline tmap_encode_fn tmap_encoder() {
+  static tmap_encode_fn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess) fn = (tmap_encode_fn)f;
+    (void)cudaGetLastError();
+  }
+  return fn;
+}
+// [rows][ld] fp16, box 64 (k) x box_rows, 128-byte swizzle, rows past the end read as zero
+inline bool make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems, uint32_t box_rows) {
+  tmap_encode_fn f = tmap_encoder();
+  if (!f) return false;
+  const cuuint64_t dims[2] = {cols, rows}, strides[1] = {ld_elems * 2u};
+  const cuuint32_t box[2] = {64u, box_rows}, el[2] = {1u, 1u};
+  return f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline bool umma_supported(const p0p_ctx*, const KP& p) {
+  if (!tmap_encoder()) return false;
+  if (p.K % 64u) return false;
+  if (p.xmode == P0P_X_CONV || p.xmode == P0P_X_CONV3) return false;
+  if (p.xmode == P0P_X_F16 && !p.vecx) return false;
+  if ((p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD) && (((uintptr_t)p.X & 15u) || p.ldx % 4u || p.kx0 % 4u)) return false;
+  if ((uintptr_t)p.W & 15u) return false;
+  if (p.enc == P0P_ENC_F16) {
+    if (!p.vecw || p.epi == P0P_EPI_SWIGLU) return false;
+  } else {
+    if (p.wR0 % 64u) return false;
+    if (p.epi == P0P_EPI_SWIGLU && (p.wR1 % 64u)) return false;
+    if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
+  }
+  return true;
+}
+
+inline int launch_umma(p0p_ctx* c, const KP& p0) {
+  KP p = p0;
+  UmmaP u{};
+  const uint32_t sms = (uint32_t)c->prop.multiProcessorCount;
+  // ---- the fused norm prologue becomes one pass into an fp16 scratch copy of the tokens
+  const void* xbase; uint64_t xld;
+  if (p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD) {
+    const uint64_t bytes = (uint64_t)p.M * p.K * 2u;
+    if (int r = ensure_scratch(c, bytes + 256)) return r;
+    const size_t n4 = (size_t)p.M * p.K / 4u;
+    k_prologue_f16<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(p, reinterpret_cast<__half*>(c->scratch));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(c, e, "prologue launch");
+    c->launches += 1;
+    xbase = c->scratch; xld = p.K;
+  } else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
+  // ---- tile shape: tokens per tile as wide as M allows; at 256 vs 128 take the one with fewer idle SM-rounds
+  uint32_t BT = 16; while (BT < 256u && BT < p.M) BT <<= 1;
+  const uint32_t ncols = p.epi == P0P_EPI_SWIGLU ? p.N : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u));
+  u.n_tiles = (ncols + 127u) / 128u;
+  if (BT == 256u) {
+    const uint64_t t256 = (uint64_t)u.n_tiles * ((p.M + 255u) / 256u), t128 = (uint64_t)u.n_tiles * ((p.M + 127u) / 128u);
+    const uint64_t cost256 = ((t256 + sms - 1) / sms) * 256u, cost128 = ((t128 + sms - 1) / sms) * 128u;
+    if (cost128 * 100u < cost256 * 90u) BT = 128;
+  }
+  u.BT = BT; u.NS = BT == 256u ? 3u : 4u;
+  u.m_tiles = (p.M + BT - 1u) / BT;
+  u.p = p; u.status = c->dev_status;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, xbase, p.K, p.M, xld, BT)) return fail(c, -12, "gemm: the token tensor map could not be encoded");
+  if (p.enc == P0P_ENC_F16) {
+    if (!make_map(&mw, reinterpret_cast<const __half*>(p.W) + p.wk0, p.K, p.Nw, p.wG, 128u)) return fail(c, -12, "gemm: the weight tensor map could not be encoded");
+  } else mw = mx;
+  const size_t qbytes = p.enc == P0P_ENC_Q4 ? U_NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? U_NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
+  // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
+  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (size_t)u.NS * U_A_BYTES + (size_t)u.NS * BT * 128u + qbytes + U_EPI_TB * 132u * 4u + 512u);
+  const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles, sms);
+  static bool ready[3] = {false, false, false};
+  cudaError_t e = cudaSuccess;
+  const int smem_max = 220 * 1024;
+  if (!ready[p.enc]) {
+    if (p.enc == P0P_ENC_Q4) e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    else if (p.enc == P0P_ENC_Q8) e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    else e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    if (e != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel attribute");
+    ready[p.enc] = true;
+  }
+  if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
+  if (p.enc == P0P_ENC_Q4) k_gemm_umma<P0P_ENC_Q4><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
+  else if (p.enc == P0P_ENC_Q8) k_gemm_umma<P0P_ENC_Q8><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
+  else k_gemm_umma<P0P_ENC_F16><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");
+  c->launches += 1;
+  return 0;
+}
+
+}  // namespace p0p

@@ -1,0 +1,51 @@
+// PTX wrappers for the 5th-generation tensor cores of sm_100a: tensor memory (TMEM) management, the
+// tcgen05.mma instruction with shared-memory operand descriptors, its commit/fence protocol, and TMEM loads.
+// Descriptor encodings follow the PTX ISA's "matrix descriptor" and "instruction descriptor" tables.
+#pragma once
+#include <stdint.h>
+
+namespace p0p {
+
+// ---- tensor memory: 512 columns x 128 lanes of 32-bit cells per SM; allocation is a whole-warp operation
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ---- shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes (64 fp16) with the
+// 128-byte swizzle: 16-byte chunk c of row r sits at r*128 + ((c ^ (r & 7)) << 4), tile base 1024-byte aligned.
+//   bits  0..13  start address >> 4          bits 16..29  leading byte offset >> 4 (1: unused for swizzled K-major)
+//   bits 32..45  stride byte offset >> 4 (1024 B between 8-row groups)      bits 46..47  version = 1
+//   bits 61..63  layout = 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// ---- instruction descriptor, kind::f16: fp16 A and B (K-major both), fp32 accumulate, M x N tile
+//   bits 4..5 D format (1 = f32)   7..9 A format (0 = f16)   10..12 B format (0 = f16)   15 / 16 A / B major (0 = K)
+//   bits 17..22 N >> 3             24..28 M >> 4
+__device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t M, uint32_t N) { return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by ONE thread
+__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// this warp's 32 lanes x 16 consecutive columns -> 16 registers per thread (thread i reads lane base + i)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace p0p

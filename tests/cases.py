@@ -35,7 +35,7 @@ def rope_table(L, seed=5):
 
 def build(c: dict) -> dict:
     """Seeded host arrays of a case.  Keys of c: enc, M, N, K, xmode, epi and the optional fields of the op."""
-    c = dict(c)
+    c = dict(c); c.pop("expect", None)
     enc = ENC_NAMES.get(c["enc"], c["enc"])
     M, N, K = c["M"], c["N"], c["K"]
     seed = c.get("seed", 7)

@@ -228,22 +228,78 @@ CONV = [
 
 
 @pytest.mark.parametrize("case", EXTRA + CONV, ids=lambda c: c["name"])
-@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("kernel", KERNELS + ["umma"])
 def test_fused_variants(gpu, oracle, case, kernel):
     h = CS.build(dict(case, kernel=kernel))
-    got = CS.run_gpu(gpu, h)
+    try:
+        got = CS.run_gpu(gpu, h)
+    except ValueError as e:
+        if kernel == "umma" and "does not take" in str(e):
+            pytest.skip("outside the tensor-core kernel's conditions")
+        raise
     want = CS.run_oracle(h)
     CS.check(got, want, case["name"])
+
+
+UMMA = [
+    dict(name="u q4 M300", enc="q4", M=300, N=384, K=512),
+    dict(name="u q8 M520 3 token tiles", enc="q8", M=520, N=256, K=1024),
+    dict(name="u f16 M200 ld", enc="f16", M=200, N=320, K=448, w_ld=456, w_cols=456, wr0=5, w_rows=330),
+    dict(name="u q4 M17", enc="q4", M=17, N=256, K=256),
+    dict(name="u f16 M3 (small M, fp16 weights)", enc="f16", M=3, N=256, K=512),
+    dict(name="u q4 many tiles (two accumulators, ring wrap)", enc="q4", M=1024, N=6144, K=320),
+    dict(name="u q8 many tiles", enc="q8", M=700, N=5120, K=192),
+    dict(name="u rms+swiglu M512", enc="q4", M=512, N=1024, K=1024, xmode="rms", epi="swiglu"),
+    dict(name="u swiglu bias rows tail", enc="q8", M=130, N=320, K=256, epi="swiglu", bias=True, wr0=64, wr1=320, w_rows=512),
+    dict(name="u lnmod+heads M300", enc="q8", M=300, N=1152, K=512, xmode="lnmod", epi="heads", heads=dict(Ltot=320, Hq=4, Hkv=2, rowOff=10, eps=1e-6)),
+    dict(name="u heads half M200", enc="q4", M=200, N=512, K=256, epi="heads", heads=dict(Ltot=200, Hq=2, Hkv=1, rowOff=0, eps=1e-6, ropeMode="half")),
+    dict(name="u resadd gate+bias M260", enc="q4", M=260, N=384, K=256, epi="resadd", gate=True, bias=True),
+    dict(name="u f32 tail columns", enc="q4", M=70, N=200, K=128, epi="f32", w_rows=256),
+    dict(name="u bias+res M90", enc="f16", M=90, N=256, K=128, epi="bias", res=True),
+    dict(name="u onormgate M64", enc="q4", M=64, N=256, K=256, epi="onormgate", Ltot=256),
+    dict(name="u sub-ranges", enc="q4", M=50, N=128, K=128, ldx=328, kx0=72, wk0=160, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="u sub-ranges q8", enc="q8", M=50, N=128, K=128, ldx=328, kx0=72, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
+]
+
+
+@pytest.mark.parametrize("case", UMMA, ids=lambda c: c["name"])
+def test_tensor_core_kernel(gpu, oracle, case):
+    """the tcgen05 / TMEM kernel against the oracle; it is also what the library picks for these shapes, and it is
+    deterministic run to run"""
+    from p0pc0rn_kernels_b200._lib import K_UMMA
+    h = CS.build(dict(case, kernel="umma"))
+    got = CS.run_gpu(gpu, h)
+    assert gpu.lastKernel == K_UMMA
+    CS.check(got, CS.run_oracle(h), case["name"])
+    got2 = CS.run_gpu(gpu, CS.build(dict(case)))
+    assert gpu.lastKernel == K_UMMA and np.array_equal(got, got2)
+
+
+def test_tensor_core_matches_general_kernel_bits_of_weights(gpu, oracle):
+    """identity tokens turn the multiply into a read-out of the operand tiles: the tensor-core kernel's dequantised
+    weights equal f16(deq) bit for bit (fp32 accumulation of one non-zero product per output is exact)"""
+    O = oracle
+    K, N = 256, 256
+    for enc in ("q4g32a.t64", "q8g64s.t64"):
+        W0 = O.randn(N * K, 11, 0.05); Wb, deq = CS.encode(enc, W0, N, K)
+        X = np.eye(K, dtype=np.float32)
+        wb, xb, yb = gpu.upload(Wb), gpu.upload(P().toF16(X)), gpu.buffer(K * N * 2)
+        try:
+            P().gemm(gpu, {"w": {"enc": enc, "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": {"buf": xb}, "y": {"buf": yb}, "M": K, "N": N, "K": K, "kernel": "umma"})
+            got = gpu.read(yb, 0, K * N * 2).view(np.uint16).reshape(K, N)
+            assert np.array_equal(got, O.to_f16(deq).reshape(N, K).T), enc
+        finally:
+            for b in (wb, xb, yb): gpu.free(b)
 
 
 DECODE = [
     dict(name="d q4 M1", enc="q4", M=1, N=256, K=512),
     dict(name="d q8 M1", enc="q8", M=1, N=256, K=512),
     dict(name="d q4 M2 long K", enc="q4", M=2, N=128, K=4096 + 1024),
-    dict(name="d q8 M3 long K", enc="q8", M=3, N=192, K=4096 + 384),
-    dict(name="d q4 M5 K384", enc="q4", M=5, N=320, K=384),
+    dict(name="d q8 M3 long K", enc="q8", M=3, N=192, K=4096 + 768),
+    dict(name="d q4 M5 K768", enc="q4", M=5, N=320, K=768),
     dict(name="d q4 M8", enc="q4", M=8, N=512, K=1024),
-    dict(name="d q8 M9", enc="q8", M=9, N=256, K=640),
+    dict(name="d q8 M9", enc="q8", M=9, N=256, K=1280),
     dict(name="d q4 M16", enc="q4", M=16, N=1024, K=2048),
     dict(name="d q8 M16", enc="q8", M=16, N=256, K=1536),
     dict(name="d q4 M13 tail cols", enc="q4", M=13, N=100, K=256, w_rows=128),
@@ -257,9 +313,10 @@ DECODE = [
     dict(name="d lnmod+heads M12", enc="q8", M=12, N=384, K=256, xmode="lnmod", epi="heads", heads=dict(Ltot=20, Hq=1, Hkv=1, rowOff=3, eps=1e-6)),
     dict(name="d heads half M5", enc="q4", M=5, N=512, K=256, epi="heads", heads=dict(Ltot=8, Hq=2, Hkv=1, rowOff=1, eps=1e-6, ropeMode="half")),
     dict(name="d onormgate M4", enc="q4", M=4, N=256, K=256, epi="onormgate", Ltot=256),
-    dict(name="d sub-ranges M4", enc="q4", M=4, N=128, K=128, ldx=320, kx0=64, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
-    dict(name="d sub-ranges q8 M4", enc="q8", M=4, N=128, K=128, ldx=328, kx0=66, wk0=128, w_cols=384, wr0=64, w_rows=256, ldy=200, ny0=40),
-    dict(name="d byte offsets M2", enc="q8", M=2, N=128, K=128, x_off=256, w_off=512, y_off=768),
+    dict(name="d sub-ranges M4", enc="q4", M=4, N=128, K=256, ldx=448, kx0=64, wk0=160, w_cols=512, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="d sub-ranges q8 M4", enc="q8", M=4, N=128, K=256, ldx=456, kx0=66, wk0=128, w_cols=512, wr0=64, w_rows=256, ldy=200, ny0=40),
+    dict(name="d byte offsets M2", enc="q8", M=2, N=128, K=256, x_off=256, w_off=512, y_off=768),
+    dict(name="d K not a stage multiple -> general kernel", enc="q4", M=2, N=128, K=384, expect="generic"),
 ]
 
 
@@ -267,6 +324,12 @@ DECODE = [
 def test_decode_kernel(gpu, oracle, case):
     """the decode-sized kernel (M <= 16: bulk-copy weight stream, raw codes on the tensor cores, split-K) against the oracle"""
     from p0pc0rn_kernels_b200._lib import K_DECODE
+    if case.get("expect") == "generic":                          # shapes the kernel does not take are refused when forced and served otherwise
+        with pytest.raises(ValueError, match="does not take"):
+            CS.run_gpu(gpu, CS.build(dict(case, kernel="decode")))
+        h = CS.build(dict(case)); got = CS.run_gpu(gpu, h)
+        CS.check(got, CS.run_oracle(h), case["name"])
+        return
     h = CS.build(dict(case, kernel="decode"))
     got = CS.run_gpu(gpu, h)
     assert gpu.lastKernel == K_DECODE
