@@ -128,12 +128,20 @@ __device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, u
 // They are plain (non-volatile) asm so that the compiler may overlap the records of a stage; `anchor` ties their
 // addresses to a point after the stage's mbarrier wait, so none of them can move above it.
 __device__ __forceinline__ uint32_t anchor(uint32_t a) { uint32_t v; asm volatile("mov.u32 %0, %1;" : "=r"(v) : "r"(a) : "memory"); return v; }
-__device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint16_t lds16(uint32_t a) { uint16_t v; asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint2 lds64(uint32_t a) { uint2 v; asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
-__device__ __forceinline__ uint4 lds128(uint32_t a) { uint4 v; asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
-__device__ __forceinline__ float2 lds64f(uint32_t a) { float2 v; asm("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v; }
-__device__ __forceinline__ float4 lds128f(uint32_t a) { float4 v; asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v; }
+// The byte offset is a template argument so that it becomes the instruction's immediate (an asm operand in a
+// register would cost one address add per load).
+template <uint32_t O> __device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(O)); return v; }
+template <uint32_t O> __device__ __forceinline__ uint16_t lds16(uint32_t a) { uint16_t v; asm("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(O)); return v; }
+template <uint32_t O> __device__ __forceinline__ uint4 lds128(uint32_t a) { uint4 v; asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(O)); return v; }
+template <uint32_t O> __device__ __forceinline__ float2 lds64f(uint32_t a) { float2 v; asm("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(a), "n"(O)); return v; }
+template <uint32_t O> __device__ __forceinline__ float4 lds128f(uint32_t a) { float4 v; asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(O)); return v; }
+// the token operand of lanes whose token column does not exist is zero: the load is predicated off for them
+template <uint32_t O> __device__ __forceinline__ uint4 lds128_if(uint32_t a, uint32_t on) {
+  uint4 v;
+  asm("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\tmov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}"
+      : "=&r"(v.x), "=&r"(v.y), "=&r"(v.z), "=&r"(v.w) : "r"(a), "r"(on), "n"(O));
+  return v;
+}
 
 // (a & mask) | magic in ONE instruction (left to the compiler this becomes two)
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t magic) {
@@ -147,6 +155,66 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
   asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// per-lane constants of the consumer loop
+struct DLane { uint32_t MLO, MHI, MAGIC; uint32_t on0, on1; bool one; };
+
+// one q4 record (64 rows x 32 k) of this warp's share of a stage: R is its index in the share
+template <int MP, uint32_t R>
+__device__ __forceinline__ void d_rec_q4(float (&tot)[MP / 8][4], uint32_t ca, uint32_t sa, uint32_t xk0, uint32_t xk1, uint32_t ck, uint32_t sk, const DLane& L) {
+  const uint32_t wl = lds32<R * 1280u>(ca), wh = lds32<R * 1280u + 128u>(ca);
+  const uint32_t sml = lds32<R * 1280u>(sa), smh = lds32<R * 1280u + 32u>(sa);
+  // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
+  const uint32_t wl8 = wl >> 8, wh8 = wh >> 8;
+  const uint32_t l0 = and_or(wl, L.MLO, L.MAGIC), h0 = and_or(wl, L.MHI, L.MAGIC), l1 = and_or(wl8, L.MLO, L.MAGIC), h1 = and_or(wl8, L.MHI, L.MAGIC);
+  const uint32_t L0 = and_or(wh, L.MLO, L.MAGIC), H0 = and_or(wh, L.MHI, L.MAGIC), L1 = and_or(wh8, L.MLO, L.MAGIC), H1 = and_or(wh8, L.MHI, L.MAGIC);
+  const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&sml)), fh = __half22float2(*reinterpret_cast<const __half2*>(&smh));   // (scale, min)
+#pragma unroll
+  for (int h = 0; h < MP / 8; h++) {
+    const uint4 b = h == 0 ? lds128_if<R * 64u>(xk0, L.on0) : lds128_if<R * 64u>(xk1, L.on1);
+    const float4 c = h == 0 ? lds128f<R * (MP / 2) * 16u>(ck) : lds128f<(R * (MP / 2) + 4u) * 16u>(ck);      // the accumulator starts at -C
+    const float2 sx = h == 0 ? lds64f<R * (MP / 2) * 8u>(sk) : lds64f<(R * (MP / 2) + 4u) * 8u>(sk);
+    const float cin[4] = {c.x, c.y, c.z, c.w};
+    float acc[4], acc2[4];
+    mma_16816(acc, l0, L0, h0, H0, b.x, b.y, cin);
+    mma_16816(acc2, l1, L1, h1, H1, b.z, b.w, acc);
+    tot[h][0] = fmaf(fl.y, sx.x, fmaf(fl.x, acc2[0], tot[h][0]));
+    tot[h][2] = fmaf(fh.y, sx.x, fmaf(fh.x, acc2[2], tot[h][2]));
+    if (!L.one) {
+      tot[h][1] = fmaf(fl.y, sx.y, fmaf(fl.x, acc2[1], tot[h][1]));
+      tot[h][3] = fmaf(fh.y, sx.y, fmaf(fh.x, acc2[3], tot[h][3]));
+    }
+  }
+}
+// one q8 record (64 rows x 64 k)
+template <int MP, uint32_t R>
+__device__ __forceinline__ void d_rec_q8(float (&tot)[MP / 8][4], uint32_t ca, uint32_t sa, uint32_t xk0, uint32_t xk1, uint32_t ck, const DLane& L) {
+  const uint4 ql = lds128<R * 4224u>(ca), qh = lds128<R * 4224u + 512u>(ca);
+  const float sl = __half2float(__ushort_as_half(lds16<R * 4224u>(sa))), sh = __half2float(__ushort_as_half(lds16<R * 4224u + 16u>(sa)));
+  const uint32_t wl[4] = {ql.x ^ 0x80808080u, ql.y ^ 0x80808080u, ql.z ^ 0x80808080u, ql.w ^ 0x80808080u};
+  const uint32_t wh[4] = {qh.x ^ 0x80808080u, qh.y ^ 0x80808080u, qh.z ^ 0x80808080u, qh.w ^ 0x80808080u};
+#pragma unroll
+  for (int h = 0; h < MP / 8; h++) {
+    // this lane's 16 columns of the record: 16*t4 .. 16*t4+15, natural order, 32 bytes
+    const uint4 b0 = h == 0 ? lds128_if<R * 128u>(xk0, L.on0) : lds128_if<R * 128u>(xk1, L.on1);
+    const uint4 b1 = h == 0 ? lds128_if<R * 128u + 16u>(xk0, L.on0) : lds128_if<R * 128u + 16u>(xk1, L.on1);
+    const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const float4 c = h == 0 ? lds128f<R * (MP / 2) * 16u>(ck) : lds128f<(R * (MP / 2) + 4u) * 16u>(ck);      // the accumulator starts at -C
+    float acc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float nx[4];
+      mma_16816(nx, __byte_perm(wl[j], 0x64646464u, 0x4140), __byte_perm(wh[j], 0x64646464u, 0x4140),
+                __byte_perm(wl[j], 0x64646464u, 0x4342), __byte_perm(wh[j], 0x64646464u, 0x4342), bb[2 * j], bb[2 * j + 1], acc);
+#pragma unroll
+      for (int i = 0; i < 4; i++) acc[i] = nx[i];
+    }
+    tot[h][0] = fmaf(sl, acc[0], tot[h][0]);
+    tot[h][1] = fmaf(sl, acc[1], tot[h][1]);
+    tot[h][2] = fmaf(sh, acc[2], tot[h][2]);
+    tot[h][3] = fmaf(sh, acc[3], tot[h][3]);
+  }
 }
 
 template <int ENC, int XMODE, int MP>
@@ -209,11 +277,16 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   // token columns past M read the row of zeros
   const uint32_t xrow0 = smem_u32(xs) + min(g, p.M) * tok_stride + half * RPW * REC_K * 2u + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
   const uint32_t xrow1 = smem_u32(xs) + min(g + 8u, p.M) * tok_stride + half * RPW * REC_K * 2u + (ENC == P0P_ENC_Q4 ? t4 * 16u : t4 * 32u);
-  const uint32_t ctc_l = smem_u32(ctc) + (half * RPW * (MP / 2) + t4) * 16u;   // this lane's token pair (2 t4, 2 t4 + 1); + 4 pairs for tokens 8..15
-  const uint32_t cts_l = smem_u32(cts) + (half * RPW * (MP / 2) + t4) * 8u;
+  // this lane's token pair (2 t4, 2 t4 + 1); + 4 pairs for tokens 8..15.  With a single token every lane reads pair 0
+  // (one address per warp instead of four)
+  const uint32_t tp = p.M == 1u ? 0u : t4;
+  const uint32_t ctc_l = smem_u32(ctc) + (half * RPW * (MP / 2) + tp) * 16u;
+  const uint32_t cts_l = smem_u32(cts) + (half * RPW * (MP / 2) + tp) * 8u;
   float* comb_l = comb + (rg * 32u + lane) * (MP / 2);
-  const uint32_t MLO = 0x000f000fu, MHI = 0x00f000f0u, MAGIC = 0x64006400u;
-  const bool one = p.M == 1u;                                            // a single token: only the accumulators of token 0 are kept up
+  DLane L;
+  L.MLO = 0x000f000fu; L.MHI = 0x00f000f0u; L.MAGIC = 0x64006400u;
+  L.on0 = g < p.M ? 1u : 0u; L.on1 = g + 8u < p.M ? 1u : 0u;            // does this lane's token column exist?
+  L.one = p.M == 1u;                                                     // a single token: only the accumulators of token 0 are kept up
   uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
   bool ok = true;
   // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
@@ -239,64 +312,17 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
       const uint32_t ca = code0 + so, sa = sm0 + so;
       const uint32_t xk0 = xrow0 + ko * 2u, xk1 = xrow1 + ko * 2u;
       const uint32_t ck = ctc_l + (ko / GS) * (MP / 2) * 16u;
-      if (d.dbg_skip) { tot[0][0] += __uint_as_float(lds32(ca)); } else
+      if (d.dbg_skip) { tot[0][0] += __uint_as_float(lds32<0>(ca)); } else
       if (ENC == P0P_ENC_Q4) {
         const uint32_t sk = cts_l + (ko / GS) * (MP / 2) * 8u;
-#pragma unroll
-        for (uint32_t r = 0; r < RPW; r++) {
-          const uint32_t wl = lds32(ca + r * 1280u), wh = lds32(ca + r * 1280u + 128u);
-          const uint32_t sml = lds32(sa + r * 1280u), smh = lds32(sa + r * 1280u + 32u);
-          // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
-          const uint32_t wl8 = wl >> 8, wh8 = wh >> 8;
-          const uint32_t l0 = and_or(wl, MLO, MAGIC), h0 = and_or(wl, MHI, MAGIC), l1 = and_or(wl8, MLO, MAGIC), h1 = and_or(wl8, MHI, MAGIC);
-          const uint32_t L0 = and_or(wh, MLO, MAGIC), H0 = and_or(wh, MHI, MAGIC), L1 = and_or(wh8, MLO, MAGIC), H1 = and_or(wh8, MHI, MAGIC);
-          const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&sml)), fh = __half22float2(*reinterpret_cast<const __half2*>(&smh));   // (scale, min)
-#pragma unroll
-          for (int h = 0; h < MP / 8; h++) {
-            const uint4 b = lds128((h == 0 ? xk0 : xk1) + r * 64u);
-            const float4 c = lds128f(ck + (r * (MP / 2) + 4 * h) * 16u);      // the accumulator starts at -C
-            const float2 sx = lds64f(sk + (r * (MP / 2) + 4 * h) * 8u);
-            const float cin[4] = {c.x, c.y, c.z, c.w};
-            float acc[4], acc2[4];
-            mma_16816(acc, l0, L0, h0, H0, b.x, b.y, cin);
-            mma_16816(acc2, l1, L1, h1, H1, b.z, b.w, acc);
-            tot[h][0] = fmaf(fl.y, sx.x, fmaf(fl.x, acc2[0], tot[h][0]));
-            tot[h][2] = fmaf(fh.y, sx.x, fmaf(fh.x, acc2[2], tot[h][2]));
-            if (!one) {
-              tot[h][1] = fmaf(fl.y, sx.y, fmaf(fl.x, acc2[1], tot[h][1]));
-              tot[h][3] = fmaf(fh.y, sx.y, fmaf(fh.x, acc2[3], tot[h][3]));
-            }
-          }
-        }
+        static_assert(D_STAGE_K == 256, "four q4 records / two q8 records per consumer warp and stage");
+        d_rec_q4<MP, 0>(tot, ca, sa, xk0, xk1, ck, sk, L);
+        d_rec_q4<MP, 1>(tot, ca, sa, xk0, xk1, ck, sk, L);
+        d_rec_q4<MP, 2>(tot, ca, sa, xk0, xk1, ck, sk, L);
+        d_rec_q4<MP, 3>(tot, ca, sa, xk0, xk1, ck, sk, L);
       } else {
-#pragma unroll
-        for (uint32_t r = 0; r < RPW; r++) {
-          const uint4 ql = lds128(ca + r * 4224u), qh = lds128(ca + r * 4224u + 512u);
-          const float sl = __half2float(__ushort_as_half(lds16(sa + r * 4224u))), sh = __half2float(__ushort_as_half(lds16(sa + r * 4224u + 16u)));
-          const uint32_t wl[4] = {ql.x ^ 0x80808080u, ql.y ^ 0x80808080u, ql.z ^ 0x80808080u, ql.w ^ 0x80808080u};
-          const uint32_t wh[4] = {qh.x ^ 0x80808080u, qh.y ^ 0x80808080u, qh.z ^ 0x80808080u, qh.w ^ 0x80808080u};
-#pragma unroll
-          for (int h = 0; h < MP / 8; h++) {
-            // this lane's 16 columns of the record: 16*t4 .. 16*t4+15, natural order, 32 bytes
-            const uint32_t bp = (h == 0 ? xk0 : xk1) + r * 128u;
-            const uint4 b0 = lds128(bp), b1 = lds128(bp + 16u);
-            const uint32_t bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            const float4 c = lds128f(ck + (r * (MP / 2) + 4 * h) * 16u);      // the accumulator starts at -C
-            float acc[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              float nx[4];
-              mma_16816(nx, __byte_perm(wl[j], 0x64646464u, 0x4140), __byte_perm(wh[j], 0x64646464u, 0x4140),
-                        __byte_perm(wl[j], 0x64646464u, 0x4342), __byte_perm(wh[j], 0x64646464u, 0x4342), bb[2 * j], bb[2 * j + 1], acc);
-#pragma unroll
-              for (int i = 0; i < 4; i++) acc[i] = nx[i];
-            }
-            tot[h][0] = fmaf(sl, acc[0], tot[h][0]);
-            tot[h][1] = fmaf(sl, acc[1], tot[h][1]);
-            tot[h][2] = fmaf(sh, acc[2], tot[h][2]);
-            tot[h][3] = fmaf(sh, acc[3], tot[h][3]);
-          }
-        }
+        d_rec_q8<MP, 0>(tot, ca, sa, xk0, xk1, ck, L);
+        d_rec_q8<MP, 1>(tot, ca, sa, xk0, xk1, ck, L);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8u * s);
