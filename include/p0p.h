@@ -141,6 +141,22 @@ int p0p_gemm(p0p_ctx* ctx, const p0p_gemm_args* a, double* flops);
 int p0p_last_kernel(const p0p_ctx* ctx);
 uint64_t p0p_launch_count(const p0p_ctx* ctx);
 
+/* No counterpart in the reference (a browser page never manages device memory).  The decode-sized q4 multiply
+ * (M <= 16 tokens: y[M][N] fp16 = x[M][K] fp16 * W^T, W in q4g32a.t64) for callers that cannot allocate on the
+ * device: hosts that hand a library no device memory at run time (a serving process that reserved the GPU for its
+ * own arena, a plug-in under another runtime's allocator, a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation).  It takes no context: w, x, y are the caller's own device pointers (16-byte aligned), work is
+ * enqueued on the caller's cudaStream_t, and it calls no allocating routine.  The kernel's split-K partial sums
+ * live in an array of P0P_STATIC_SCRATCH_BYTES built into the library's device image (every GPU that loads the
+ * library holds it until the process exits); a shape that needs more (roughly 4 * M * N * ceil(K / 1024) bytes)
+ * is refused with a message in `err`.  All calls on a device share that array: calls whose kernels overlap on
+ * the GPU race, so keep them in one stream order.  The first call on each device resolves the array's device
+ * address; make it before any stream capture.  Conditions: 1 <= M <= 16, N % 64 == 0, K % 256 == 0.
+ * Returns 0, < 0 for refused arguments, > 0 for a CUDA error; `err` (optional) receives the reason. */
+#define P0P_STATIC_SCRATCH_BYTES (8u << 20)
+int p0p_decode_q4_static(int device, void* stream, const void* w, const void* x, void* y, uint32_t M, uint32_t N, uint32_t K,
+                         char* err, size_t err_cap);
+
 /* Debug op: writes the fp16 tile values the kernels feed to the multiply, rows [r0, r0+nr) x all w_cols
  * columns, row-major into `out` (fp16).  path 0 = the fp32-FMA conversion, 1 = the packed half2 conversion
  * the tensor-core kernels use.  Both must equal f16(q*s+min) / f16(q*s) of docs/FORMAT.md bit for bit. */
