@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
         const uint32_t r0 = d_tile_row0(d, t);
         const unsigned char* src = p.W + ((size_t)(r0 >> 6) * p.wG + (p.wk0 + k_beg) / REC_K) * REC;
         for (uint32_t k = 0; k < klen; k += D_STAGE_K, src += STAGE_TX) {
-          if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, d.status, 101)) return;
+          if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, d.status, 101, 200u)) return;
           mbar_expect_tx(full0 + 8u * s, STAGE_TX);
           bulk_g2s(smem_u32(stages + s * D_STAGE_BYTES), src, STAGE_TX, full0 + 8u * s);
           if (++s == D_STAGES) { s = 0; ph ^= 1u; }

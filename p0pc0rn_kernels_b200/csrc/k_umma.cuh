@@ -30,8 +30,8 @@
 
 namespace p0p {
 
-constexpr int U_THREADS = 448;           // 14 warps
-constexpr int U_NQ = 4;                  // stages of quantised records
+constexpr int U_THREADS = 480;           // 15 warps
+constexpr int U_NQ_MAX = 8;              // most stages of quantised records
 constexpr int U_A_BYTES = 128 * 128;     // one weight operand stage: 128 rows x 64 fp16
 constexpr int U_EPI_TB = 16;             // tokens per epilogue pass
 constexpr int U_TMEM_COLS = 512;
@@ -40,42 +40,59 @@ struct UmmaP {
   KP p;
   uint32_t BT;          // tokens per tile (UMMA N): 16, 32, 64, 128 or 256
   uint32_t NS;          // operand stages (3 or 4)
+  uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
   int* status;
 };
 
-template <int ENC> struct UQ { static constexpr uint32_t REC = 0, REC_K = 64, RB = 0, STAGE = 0; };
-template <> struct UQ<P0P_ENC_Q4> { static constexpr uint32_t REC = 1280, REC_K = 32, RB = 2560, STAGE = 5248; };   // 2 x (2 records) + 64 B pad between the record tiles
-template <> struct UQ<P0P_ENC_Q8> { static constexpr uint32_t REC = 4224, REC_K = 64, RB = 4224, STAGE = 8576; };
+// A stage of quantised records covers KSUP k-steps (64 k each) of both 64-row record tiles of the block's 128 rows:
+// two bulk copies of KSUP * RB bytes (the records of one row tile are consecutive along K), 64 bytes apart in
+// shared memory so that the two tiles fall into different banks.  Large copies matter: the copy engine's request
+// rate, not its byte rate, bounds many small copies.
+template <int ENC> struct UQ { static constexpr uint32_t REC = 0, REC_K = 64, RB = 0, KSUP = 1, STAGE = 0; };
+template <> struct UQ<P0P_ENC_Q4> { static constexpr uint32_t REC = 1280, REC_K = 32, RB = 2560, KSUP = 4, STAGE = 2 * 4 * 2560 + 128; };
+template <> struct UQ<P0P_ENC_Q8> { static constexpr uint32_t REC = 4224, REC_K = 64, RB = 4224, KSUP = 2, STAGE = 2 * 2 * 4224 + 128; };
 
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) { asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
 __device__ __forceinline__ uint4 u_lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint32_t u_lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint16_t u_lds16(uint32_t a) { uint16_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory"); return v; }
 
-template <int ENC>
+// ring position that wraps without division
+struct Ring {
+  uint32_t s = 0, ph = 0, n;
+  __device__ __forceinline__ explicit Ring(uint32_t n_) : n(n_) {}
+  __device__ __forceinline__ void next() { if (++s == n) { s = 0; ph ^= 1u; } }
+};
+
+// ATM: the dequantised weight operand lives in tensor memory (written with tcgen05.st) instead of shared memory.
+// Shared-memory bandwidth is what bounds the kernel otherwise: per 64-k step a 128 x 64 fp16 tile would be
+// written once and read once there, on top of the token tile and the records.  Tensor memory then holds two
+// accumulators of up to 192 columns and four 32-column operand stages (2 x 192 + 4 x 32 = 512).
+constexpr uint32_t U_ACC_STRIDE_ATM = 192, U_A_COL0_ATM = 384;
+template <int ENC, bool ATM>
 __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW) {
   extern __shared__ unsigned char smem_raw[];
   const KP& p = u.p;
-  const uint32_t BT = u.BT, NS = u.NS;
+  const uint32_t BT = u.BT, NS = u.NS, NQ = u.NQ;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                     // operand tiles need 1024-byte alignment
   unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t a_st = base, x_st = a_st + NS * U_A_BYTES, q_st = x_st + NS * BT * 128u;
-  const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : U_NQ * UQ<ENC>::STAGE);
+  const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * BT * 128u;
+  const uint32_t acc_stride = ATM ? U_ACC_STRIDE_ATM : 256u;
+  const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * UQ<ENC>::STAGE);
   const uint32_t bars = epi_sh + U_EPI_TB * 132u * 4u;
   float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
-  // barrier slots (8 bytes each)
-  const uint32_t a_full = bars, x_full = a_full + 8u * 4u, ab_empty = x_full + 8u * 4u, wq_full = ab_empty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ;
-  const uint32_t acc_full = wq_empty + 8u * U_NQ, acc_empty = acc_full + 16u, tmem_slot = acc_empty + 16u;
+  // barrier slots (8 bytes each): operands of a stage ready / stage free / record stage ready / record stage free / accumulator ready / free
+  const uint32_t full = bars, empty = full + 8u * 4u, wq_full = empty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ_MAX;
+  const uint32_t acc_full = wq_empty + 8u * U_NQ_MAX, acc_empty = acc_full + 16u, tmem_slot = acc_empty + 16u;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   if (tid == 0) {
     for (uint32_t s = 0; s < 4u; s++) {
-      mbar_init(a_full + 8u * s, ENC == P0P_ENC_F16 ? 1u : 8u);
-      mbar_init(x_full + 8u * s, 1u);
-      mbar_init(ab_empty + 8u * s, 1u);
+      mbar_init(full + 8u * s, ENC == P0P_ENC_F16 ? 1u : 5u);     // the producer's expect_tx arrival (+ the four warps of a dequant group)
+      mbar_init(empty + 8u * s, 1u);
     }
-    for (uint32_t s = 0; s < (uint32_t)U_NQ; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, 8u); }
+    for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, 8u); }
     for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
     fence_mbar_init();
   }
@@ -89,35 +106,40 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   const bool swiglu = p.epi == P0P_EPI_SWIGLU;
 
   if (warp == 0) {
-    // ================================================================= producer
+    // ================================================================= producer of the token tiles (and fp16 weight tiles)
     if (lane == 0) {
-      uint32_t it = 0, itq = 0;
+      Ring r(NS);
       bool ok = true;
       for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles;
-        uint32_t trow[2];
-        if (ENC != P0P_ENC_F16) {
-          const uint32_t last = (p.Nw >> 6) - 1u;              // record tiles past the weight's end do not exist: their columns are never stored
-          if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
-          else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
+        for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
+          if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
+          mbar_expect_tx(full + 8u * r.s, BT * 128u + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u));
+          tma_load_2d(x_st + r.s * BT * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT), full + 8u * r.s);
+          if (ENC == P0P_ENC_F16) tma_load_2d(a_st + r.s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), full + 8u * r.s);
         }
-        for (uint32_t ks = 0; ks < KS; ks++, it++) {
-          const uint32_t s = it % NS, ph = (it / NS) & 1u;
-          if (!mbar_wait(ab_empty + 8u * s, ph ^ 1u, u.status, 201)) { ok = false; break; }
-          mbar_expect_tx(x_full + 8u * s, BT * 128u);
-          tma_load_2d(x_st + s * BT * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT), x_full + 8u * s);
-          if (ENC == P0P_ENC_F16) {
-            mbar_expect_tx(a_full + 8u * s, U_A_BYTES);
-            tma_load_2d(a_st + s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), a_full + 8u * s);
-          } else {
-            const uint32_t sq = itq % U_NQ, phq = (itq / U_NQ) & 1u;
-            if (!mbar_wait(wq_empty + 8u * sq, phq ^ 1u, u.status, 202)) { ok = false; break; }
-            mbar_expect_tx(wq_full + 8u * sq, 2u * UQ<ENC>::RB);
-            const size_t koff = (size_t)((p.wk0 + ks * 64u) / UQ<ENC>::REC_K) * UQ<ENC>::REC;
-            bulk_g2s(q_st + sq * UQ<ENC>::STAGE, p.W + (size_t)trow[0] * p.wG * UQ<ENC>::REC + koff, UQ<ENC>::RB, wq_full + 8u * sq);
-            bulk_g2s(q_st + sq * UQ<ENC>::STAGE + UQ<ENC>::RB + 64u, p.W + (size_t)trow[1] * p.wG * UQ<ENC>::REC + koff, UQ<ENC>::RB, wq_full + 8u * sq);
-            itq++;
-          }
+      }
+    }
+  } else if (warp == 14) {
+    // ================================================================= producer of the quantised records: runs ahead of
+    // everything else by NQ stages (its only wait is for a free record stage)
+    if (ENC != P0P_ENC_F16 && lane == 0) {
+      Ring q(NQ);
+      bool ok = true;
+      const uint32_t last = (p.Nw >> 6) - 1u;                  // record tiles past the weight's end do not exist: their columns are never stored
+      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const uint32_t nt = tile / u.m_tiles;
+        uint32_t trow[2];
+        if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
+        else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
+        const unsigned char* src0 = p.W + ((size_t)trow[0] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
+        const unsigned char* src1 = p.W + ((size_t)trow[1] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
+        for (uint32_t ks = 0; ks < KS; ks += UQ<ENC>::KSUP, q.next()) {
+          const uint32_t bytes = min(UQ<ENC>::KSUP, KS - ks) * UQ<ENC>::RB;
+          if (!mbar_wait(wq_empty + 8u * q.s, q.ph ^ 1u, u.status, 202, 500u)) { ok = false; break; }
+          mbar_expect_tx(wq_full + 8u * q.s, 2u * bytes);
+          bulk_g2s(q_st + q.s * UQ<ENC>::STAGE, src0 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
+          bulk_g2s(q_st + q.s * UQ<ENC>::STAGE + UQ<ENC>::KSUP * UQ<ENC>::RB + 64u, src1 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
         }
       }
     }
@@ -125,21 +147,28 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     // ================================================================= MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16(128u, BT);
-      uint32_t it = 0, tl = 0;
+      Ring r(NS);
+      uint32_t tl = 0;
       bool ok = true;
       for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, tl++) {
         const uint32_t buf = tl & 1u;
-        if (!mbar_wait(acc_empty + 8u * buf, ((tl >> 1) & 1u) ^ 1u, u.status, 203)) { ok = false; break; }
+        if (!mbar_wait(acc_empty + 8u * buf, ((tl >> 1) & 1u) ^ 1u, u.status, 203, 100u)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * 256u;
-        for (uint32_t ks = 0; ks < KS; ks++, it++) {
-          const uint32_t s = it % NS, ph = (it / NS) & 1u;
-          if (!mbar_wait(a_full + 8u * s, ph, u.status, 204) || !mbar_wait(x_full + 8u * s, ph, u.status, 205)) { ok = false; break; }
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
+          if (!mbar_wait(full + 8u * r.s, r.ph, u.status, 204)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t ad = umma_desc_sw128(a_st + s * U_A_BYTES), bd = umma_desc_sw128(x_st + s * BT * 128u);
+          const uint64_t bd = umma_desc_sw128(x_st + r.s * BT * 128u);
+          if (ATM) {
+            const uint32_t at = tmem_base + U_A_COL0_ATM + r.s * 32u;
 #pragma unroll
-          for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);   // +32 bytes (>>4) per 16 k
-          umma_commit(ab_empty + 8u * s);
+            for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ts(d_tmem, at + 8u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);          // 8 columns / +32 bytes per 16 k
+          } else {
+            const uint64_t ad = umma_desc_sw128(a_st + r.s * U_A_BYTES);
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);   // +32 bytes (>>4) per 16 k
+          }
+          umma_commit(empty + 8u * r.s);
         }
         if (ok) umma_commit(acc_full + 8u * buf);
       }
@@ -151,13 +180,13 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     bool ok = true;
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, tl++) {
       const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles, buf = tl & 1u;
-      if (ok && !mbar_wait(acc_full + 8u * buf, (tl >> 1) & 1u, u.status, 206)) ok = false;
+      if (ok && !mbar_wait(acc_full + 8u * buf, (tl >> 1) & 1u, u.status, 206, 1000u)) ok = false;
       tc_fence_after();
       const uint32_t m0 = mt * BT, nchunks = min(BT, p.M - m0 + (U_EPI_TB - 1u)) / U_EPI_TB;
       for (uint32_t ch = 0; ch < nchunks; ch++) {           // uniform over the four warps: the epilogue's named barrier needs all 128 threads
         uint32_t r[16];
         float acc[U_EPI_TB];
-        if (ok) { tmem_ld16(tmem_base + ((q * 32u) << 16) + buf * 256u + ch * U_EPI_TB, r); tmem_ld_wait(); }
+        if (ok) { tmem_ld16(tmem_base + ((q * 32u) << 16) + buf * acc_stride + ch * U_EPI_TB, r); tmem_ld_wait(); }
 #pragma unroll
         for (int j = 0; j < U_EPI_TB; j++) acc[j] = ok ? __uint_as_float(r[j]) : 0.0f;
         epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2);
@@ -166,51 +195,79 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
     }
-  } else if (ENC != P0P_ENC_F16) {
-    // ================================================================= dequantisation: codes -> swizzled fp16 operand rows
-    const uint32_t dw = warp - 6u;
-    uint32_t r, kh;                                        // this thread's operand row and which 32 k of the step
-    if (ENC == P0P_ENC_Q4) { r = (dw & 3u) * 32u + lane; kh = dw >> 2; }
-    else { r = dw * 16u + (lane >> 1); kh = lane & 1u; }
+  } else if (ENC != P0P_ENC_F16 && warp < 14) {
+    // ================================================================= dequantisation: codes -> swizzled fp16 operand rows.
+    // Two groups of four warps take alternate k-steps; a thread converts one whole operand row (64 k) of a step.
+    const uint32_t dw = warp - 6u, grp = dw >> 2, r = (warp & 3u) * 32u + lane;      // a warp reaches the tensor-memory lanes 32 * (warp % 4) .. + 31
     const uint32_t tsel = swiglu ? (r & 1u) : (r >> 6), rr = swiglu ? (r >> 1) : (r & 63u);
-    const uint32_t rsw = r & 7u, arow = r * 128u;
-    uint32_t it = 0, itq = 0;
+    const uint32_t rsw = r & 7u;
+    const uint32_t rec_row = tsel * (UQ<ENC>::KSUP * UQ<ENC>::RB + 64u) + (ENC == P0P_ENC_Q4 ? rr * 16u : rr * 64u);
+    const uint32_t rec_sm = tsel * (UQ<ENC>::KSUP * UQ<ENC>::RB + 64u) + (ENC == P0P_ENC_Q4 ? 1024u + rr * 4u : 4096u + rr * 2u);
+    Ring ar(NS), qr(NQ);
+    uint32_t sub = 0, turn = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      for (uint32_t ks = 0; ks < KS; ks++, it++, itq++) {
-        const uint32_t sq = itq % U_NQ, phq = (itq / U_NQ) & 1u, s = it % NS, ph = (it / NS) & 1u;
-        if (!mbar_wait(wq_full + 8u * sq, phq, u.status, 207) || !mbar_wait(ab_empty + 8u * s, ph ^ 1u, u.status, 208)) { ok = false; break; }
-        const uint32_t rec = q_st + sq * UQ<ENC>::STAGE + tsel * (UQ<ENC>::RB + 64u);
-        const uint32_t dst = a_st + s * U_A_BYTES + arow;
-        __half2 v[16];
-        if (ENC == P0P_ENC_Q4) {
-          const uint4 cq = u_lds128(rec + kh * 1280u + rr * 16u);
-          const uint32_t sm = u_lds32(rec + kh * 1280u + 1024u + rr * 4u);
-          const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
-          if (__all_sync(0xffffffffu, q4_pair_exact(sm))) {
-            const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+      for (uint32_t ks = 0; ks < KS; ks++) {
+        const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == KS - 1u;
+        if (turn == grp) {
+          if (!mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
+          const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + sub * UQ<ENC>::RB;
+          const uint32_t dst = a_st + ar.s * U_A_BYTES + r * 128u;
+          if (ENC == P0P_ENC_Q4) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
+            for (uint32_t kh = 0; kh < 2u; kh++) {
+              __half2 v[16];
+              const uint4 cq = u_lds128(rec + rec_row + kh * 1280u);
+              const uint32_t sm = u_lds32(rec + rec_sm + kh * 1280u);
+              const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
+              if (__all_sync(0xffffffffu, q4_pair_exact(sm))) {
+                const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+#pragma unroll
+                for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
+              } else {
+                const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+              }
+              if (ATM) {
+                tmem_st16(tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM + ar.s * 32u + kh * 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
+              } else {
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; j++) sts128(dst + (((kh * 4u + j) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[j]);
+              }
+            }
           } else {
-            const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
+            const __half2 s2 = __half2half2(__ushort_as_half(u_lds16(rec + rec_sm)));
+            // shared-memory operand: each row pair starts at another 16-byte chunk (no bank conflicts).  Tensor-memory
+            // operand: the store's column must be the same in every lane, so all lanes walk the chunks in order.
+            const uint32_t rot = ATM ? 0u : (rr >> 1) & 3u;
 #pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+            for (uint32_t jj = 0; jj < 4u; jj++) {
+              const uint32_t j = (jj + rot) & 3u;                    // 16 codes = two output chunks
+              const uint4 cq = u_lds128(rec + rec_row + j * 16u);
+              const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
+              __half2 v[8];
+#pragma unroll
+              for (int i = 0; i < 4; i++) q8_word_to_half2x2(w[i], s2, v + 2 * i);
+              if (ATM) {
+                uint32_t t8[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) t8[i] = *reinterpret_cast<const uint32_t*>(&v[i]);
+                tmem_st8(tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM + ar.s * 32u + j * 8u, t8);
+              } else {
+                sts128(dst + (((2u * j) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[0]);
+                sts128(dst + (((2u * j + 1u) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[1]);
+              }
+            }
           }
-        } else {
-          const uint32_t rot = (r >> 1) & 1u;                       // alternate the chunk order between row pairs: no bank conflicts
-          const uint32_t cb = rec + rr * 64u + kh * 32u;
-          const uint4 q0 = u_lds128(cb + rot * 16u), q1 = u_lds128(cb + (rot ^ 1u) * 16u);
-          const uint4 qa = rot ? q1 : q0, qb = rot ? q0 : q1;
-          const __half2 s2 = __half2half2(__ushort_as_half(u_lds16(rec + 4096u + rr * 2u)));
-          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-          for (int i = 0; i < 8; i++) q8_word_to_half2x2(w[i], s2, v + 2 * i);
+          if (ATM) { tmem_st_wait(); tc_fence_before(); }           // tensor-memory stores done and ordered before the MMA warp's read
+          else fence_proxy_async();                                   // generic-proxy stores -> visible to the tensor core's async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full + 8u * ar.s);
         }
-#pragma unroll
-        for (uint32_t j = 0; j < 4u; j++) sts128(dst + (((kh * 4u + j) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[j]);
-        fence_proxy_async();                                        // generic-proxy stores -> visible to the tensor core's async proxy
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(a_full + 8u * s); mbar_arrive(wq_empty + 8u * sq); }
+        // every warp walks every k-step, so it releases each record stage exactly once, after its own last use of it
+        if (last_sub) { __syncwarp(); if (lane == 0) mbar_arrive(wq_empty + 8u * qr.s); qr.next(); sub = 0; } else sub++;
+        ar.next(); turn ^= 1u;
       }
     }
   }
@@ -295,16 +352,29 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
     c->launches += 1;
     xbase = c->scratch; xld = p.K;
   } else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
-  // ---- tile shape: tokens per tile as wide as M allows; at 256 vs 128 take the one with fewer idle SM-rounds
-  uint32_t BT = 16; while (BT < 256u && BT < p.M) BT <<= 1;
-  const uint32_t ncols = p.epi == P0P_EPI_SWIGLU ? p.N : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u));
+  // ---- tile shape.  Quantised weights: operand in tensor memory, up to 192 tokens per tile; fp16 weights: both
+  // operands in shared memory, up to 256.  Within that, the width that leaves the fewest idle SM-rounds.
+  static const bool force_ss = [] { const char* e = getenv("P0P_UMMA_SS"); return e && e[0] == '1'; }();
+  const bool atm = p.enc != P0P_ENC_F16 && !force_ss;
+  const uint32_t ncols = (p.epi == P0P_EPI_SWIGLU || p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u);
   u.n_tiles = (ncols + 127u) / 128u;
-  if (BT == 256u) {
-    const uint64_t t256 = (uint64_t)u.n_tiles * ((p.M + 255u) / 256u), t128 = (uint64_t)u.n_tiles * ((p.M + 127u) / 128u);
-    const uint64_t cost256 = ((t256 + sms - 1) / sms) * 256u, cost128 = ((t128 + sms - 1) / sms) * 128u;
-    if (cost128 * 100u < cost256 * 90u) BT = 128;
+  const uint32_t bt_max = atm ? 192u : 256u;
+  uint32_t BT;
+  if (p.M <= bt_max) BT = std::max(16u, (p.M + 15u) & ~15u);
+  else {
+    uint64_t best = ~0ull; BT = bt_max;
+    for (uint32_t cand = bt_max; cand >= 128u; cand -= 16u) {
+      // a k-step costs about the same for any width up to ~320 tokens (the dequantisation bounds it), so fewer rounds win
+      const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand), cost = ((t + sms - 1) / sms) * std::max(cand, atm ? 320u : 192u);
+      if (cost < best) { best = cost; BT = cand; }
+    }
   }
-  u.BT = BT; u.NS = BT == 256u ? 3u : 4u;
+  u.BT = BT; u.NS = (!atm && BT > 192u) ? 3u : 4u;
+  // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
+  const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
+  const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + U_EPI_TB * 132u * 4u + 512u;
+  u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (100 * 1024 + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
+  if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
   u.m_tiles = (p.M + BT - 1u) / BT;
   u.p = p; u.status = c->dev_status;
   CUtensorMap mx, mw;
@@ -312,24 +382,26 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if (p.enc == P0P_ENC_F16) {
     if (!make_map(&mw, reinterpret_cast<const __half*>(p.W) + p.wk0, p.K, p.Nw, p.wG, 128u)) return fail(c, -12, "gemm: the weight tensor map could not be encoded");
   } else mw = mx;
-  const size_t qbytes = p.enc == P0P_ENC_Q4 ? U_NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? U_NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
+  const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
-  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (size_t)u.NS * U_A_BYTES + (size_t)u.NS * BT * 128u + qbytes + U_EPI_TB * 132u * 4u + 512u);
+  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + U_EPI_TB * 132u * 4u + 512u);
   const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles, sms);
-  static bool ready[3] = {false, false, false};
-  cudaError_t e = cudaSuccess;
-  const int smem_max = 220 * 1024;
-  if (!ready[p.enc]) {
-    if (p.enc == P0P_ENC_Q4) e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-    else if (p.enc == P0P_ENC_Q8) e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-    else e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-    if (e != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel attribute");
-    ready[p.enc] = true;
-  }
+  const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
-  if (p.enc == P0P_ENC_Q4) k_gemm_umma<P0P_ENC_Q4><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
-  else if (p.enc == P0P_ENC_Q8) k_gemm_umma<P0P_ENC_Q8><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
-  else k_gemm_umma<P0P_ENC_F16><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
+  static bool ready = false;
+  cudaError_t e = cudaSuccess;
+  if (!ready) {
+    if ((e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_Q8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(k_gemm_umma<P0P_ENC_F16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)) != cudaSuccess)
+      return cuda_fail(c, e, "tensor-core kernel attribute");
+    ready = true;
+  }
+  if (p.enc == P0P_ENC_Q4) { if (atm) k_gemm_umma<P0P_ENC_Q4, true><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw); else k_gemm_umma<P0P_ENC_Q4, false><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw); }
+  else if (p.enc == P0P_ENC_Q8) { if (atm) k_gemm_umma<P0P_ENC_Q8, true><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw); else k_gemm_umma<P0P_ENC_Q8, false><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw); }
+  else k_gemm_umma<P0P_ENC_F16, false><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");
   c->launches += 1;
   return 0;

@@ -22,12 +22,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// bounded wait; false after the limit (the code lands in *status)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// bounded wait; false after the limit (the code lands in *status).  sleep_ns > 0: the thread backs off between
+// polls, for waits that are long and off the critical path (a polling warp otherwise takes issue slots from the
+// warps that work).  The clock is read only every 256 polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, uint32_t sleep_ns = 0) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
+  uint32_t n = 0;
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) { if (status) atomicCAS(status, 0, code); return false; }
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((++n & 255u) == 0u && clock64() - t0 > WAIT_LIMIT_CYCLES) { if (status) atomicCAS(status, 0, code); return false; }
   }
   return true;
 }
