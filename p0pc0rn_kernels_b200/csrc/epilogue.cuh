@@ -80,16 +80,18 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     return;
   }
   if (epi == P0P_EPI_SWIGLU) {
-    const uint32_t o = col >> 1;
+    // even lanes hold 'gate', odd lanes 'up' of output column o.  The pair splits the tokens: the even lane
+    // finishes tokens j = 0, 2, .., the odd lane j = 1, 3, .., each getting the other half of its pair by one shuffle.
+    const uint32_t o = col >> 1, odd = c & 1u;
     float gB = 0.0f, uB = 0.0f;
     if ((p.flags & P0P_F_BIAS) && col < p.N) { gB = __ldg(p.BV + p.bvOff + o); uB = __ldg(p.BV + p.bvOff + p.bvUp + o); }
 #pragma unroll
-    for (int j = 0; j < TB; j++) {
-      const float up = __shfl_xor_sync(0xffffffffu, acc[j], 1);      // odd columns carry 'up'
-      const uint32_t m = m0 + j;
-      if (!(c & 1u) && m < p.M && col < p.N) {
-        const float g = acc[j] + gB, u = up + uB;
-        const float a = (p.flags & P0P_F_GELU) ? gelu_tanh(g) : silu_exact(g);
+    for (int j = 0; j < TB; j += 2) {
+      const float other = __shfl_xor_sync(0xffffffffu, odd ? acc[j] : acc[j + 1], 1);
+      const float g = (odd ? other : acc[j]) + gB, u = (odd ? acc[j + 1] : other) + uB;
+      const uint32_t m = m0 + j + odd;
+      if (m < p.M && col < p.N) {
+        const float a = (p.flags & P0P_F_GELU) ? gelu_tanh(g) : __fdividef(g, 1.0f + __expf(-g));     // hardware exp / reciprocal: a few ulp, far inside the fp16 rounding
         Yh[(size_t)m * p.ldy + p.ny0 + o] = __float2half_rn(a * u);
       }
     }
@@ -101,6 +103,15 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     if (p.flags & P0P_F_GATE) gate = __ldg(p.EV + p.evOff + col);
     if (p.flags & P0P_F_BIAS) bias = __ldg(p.BV + p.bvOff + col);
   } else if (epi == P0P_EPI_BIAS) bias = __ldg(p.EV + p.evOff + col);
+  // read-modify-write epilogues fetch all TB old values first (TB loads in flight), then add and store
+  float old[TB];
+  const bool rmw32 = epi == P0P_EPI_RESADD && !(p.flags & P0P_F_STORE), rmw16 = epi == P0P_EPI_BIAS && (p.flags & P0P_F_RES);
+#pragma unroll
+  for (int j = 0; j < TB; j++) {
+    const uint32_t m = m0 + j;
+    const size_t yi = (size_t)min(m, p.M - 1u) * p.ldy + p.ny0 + col;
+    old[j] = rmw32 ? __ldcg(Yf + yi) : rmw16 ? __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(Yh) + yi))) : 0.0f;
+  }
 #pragma unroll
   for (int j = 0; j < TB; j++) {
     const uint32_t m = m0 + j;
@@ -109,8 +120,8 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     const float a = acc[j];
     if (epi == P0P_EPI_F16) Yh[yi] = __float2half_rn(a);
     else if (epi == P0P_EPI_F32) Yf[yi] = a;
-    else if (epi == P0P_EPI_RESADD) { const float v = gate * (a + bias); Yf[yi] = (p.flags & P0P_F_STORE) ? v : Yf[yi] + v; }
-    else { float v = a + bias; if (p.flags & P0P_F_RES) v += __half2float(Yh[yi]); Yh[yi] = __float2half_rn(v); }
+    else if (epi == P0P_EPI_RESADD) Yf[yi] = old[j] + gate * (a + bias);
+    else Yh[yi] = __float2half_rn(a + bias + old[j]);
   }
 }
 

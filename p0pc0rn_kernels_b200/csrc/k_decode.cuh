@@ -44,7 +44,6 @@ struct DecodeP {
   uint32_t nslots;    // tiles * 64
   float* scratch;     // [S][M][nslots] fp32
   int* status;
-  int dbg_skip;
 };
 
 // weight tile index (64 rows) of unit-local tile t
@@ -312,7 +311,6 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
       const uint32_t ca = code0 + so, sa = sm0 + so;
       const uint32_t xk0 = xrow0 + ko * 2u, xk1 = xrow1 + ko * 2u;
       const uint32_t ck = ctc_l + (ko / GS) * (MP / 2) * 16u;
-      if (d.dbg_skip) { tot[0][0] += __uint_as_float(lds32<0>(ca)); } else
       if (ENC == P0P_ENC_Q4) {
         const uint32_t sk = cts_l + (ko / GS) * (MP / 2) * 8u;
         static_assert(D_STAGE_K == 256, "four q4 records / two q8 records per consumer warp and stage");
@@ -430,7 +428,6 @@ inline int launch_decode(p0p_ctx* c, const KP& p) {
   if (int r = ensure_scratch(c, sbytes + 256)) return r;
   d.scratch = reinterpret_cast<float*>(c->scratch);
   d.status = c->dev_status;
-  { const char* e = getenv("P0P_DECODE_SKIP"); d.dbg_skip = e && e[0] == '1'; }
   const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
   const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 16u;
   const size_t smem = (size_t)D_STAGES * (p.enc == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8) + (((p.M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;

@@ -354,8 +354,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   } else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
   // ---- tile shape.  Quantised weights: operand in tensor memory, up to 192 tokens per tile; fp16 weights: both
   // operands in shared memory, up to 256.  Within that, the width that leaves the fewest idle SM-rounds.
-  static const bool force_ss = [] { const char* e = getenv("P0P_UMMA_SS"); return e && e[0] == '1'; }();
-  const bool atm = p.enc != P0P_ENC_F16 && !force_ss;
+  const bool atm = p.enc != P0P_ENC_F16;
   const uint32_t ncols = (p.epi == P0P_EPI_SWIGLU || p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u);
   u.n_tiles = (ncols + 127u) / 128u;
   const uint32_t bt_max = atm ? 192u : 256u;

@@ -83,7 +83,7 @@ extern "C" int p0p_decode_q4_static(int device, void* stream, const void* w, con
              (unsigned long long)need, (unsigned long long)P0P_STATIC_SCRATCH_BYTES);
     return say(err, err_cap, -4, msg);
   }
-  d.scratch = pd.scratch; d.status = pd.status; d.dbg_skip = 0;
+  d.scratch = pd.scratch; d.status = pd.status;
   const uint32_t tok_stride = d.KC * 2u + 64u;
   const size_t ct_bytes = (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u;
   const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES_Q4 + (((M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
