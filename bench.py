@@ -123,7 +123,7 @@ def run_reference(args, rank):
     """--impl reference: the reference's own CPU implementation of the path (oracle port; the reference is JavaScript
     and no JavaScript engine exists here), all host threads, bounded sample per step."""
     if rank != 0:
-        return
+        os._exit(0)
     import oracle as O
     O.build()
     thr = O.max_threads()
@@ -186,7 +186,9 @@ def run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world):
                               "weight_copies": copies}), flush=True)
         for b in Ws + [xb, yb]: gpu.free(b)
         gpu.drainPool()
-    gpu.close()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def main():
@@ -332,6 +334,12 @@ def main():
     ms = timed(M, args.steps, max(3, args.warmup))
     n_launch = launches["n"]
     gu_ms, gu_kernel = kernel_ms(M, "gate_up", max(20, min(100, args.steps)))
+    # keep the GPU under the same load until the sampler (200 ms period) has a few readings of the clocks
+    t_end = time.time() + 1.2
+    gs_load = graphs_of(lambda i: block(M, i, True))
+    while time.time() < t_end:
+        for s in range(50): gs_load[s % args.copies].replay()
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     value = block_flops(M) / (ms * 1e-3) / 1e12
 
@@ -400,11 +408,14 @@ def main():
                           "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)"},
                "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
                "GB/s": block_bytes(M) / (ms * 1e-3) / 1e9}
-        print(json.dumps(out))
-    lib.p0p_host_free(gpu._h, hp)
+        print(json.dumps(out), flush=True)
+    # leave without tearing down: CUDA graphs that hold NCCL kernels and the process group do not unwind in a safe
+    # order, and a benchmark has nothing to save
+    torch.cuda.synchronize()
     if world > 1:
-        dist.barrier(); dist.destroy_process_group()
-    gpu.close()
+        dist.barrier()
+    sys.stdout.flush(); sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
