@@ -33,6 +33,12 @@ __device__ __forceinline__ float gelu_tanh(float g) {   // src/ops/gemm.js:208
   t = fminf(fmaxf(t, -15.0f), 15.0f);
   return g * 0.5f * (1.0f + tanhf(t));
 }
+// the same function through 0.5 (1 + tanh t) = 1 / (1 + e^-2t), with the hardware exponential and reciprocal
+__device__ __forceinline__ float gelu_tanh_fast(float g) {
+  float t = 0.7978845608f * (g + 0.044715f * g * g * g);
+  t = fminf(fmaxf(t, -15.0f), 15.0f);
+  return __fdividef(g, 1.0f + __expf(-2.0f * t));
+}
 
 // ---- weight decoding, one value (docs/FORMAT.md; index arithmetic of src/ops/gemm.js:143-171) ---------
 // fp32 multiply-add then one rounding to fp16: q*s is exact in fp32, so this is f16(f32(q*s + min)).

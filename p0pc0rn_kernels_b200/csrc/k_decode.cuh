@@ -387,6 +387,7 @@ inline bool decode_supported(const KP& p) {
   if (p.K % D_STAGE_K) return false;                  // k-blocks are whole stages
   if ((uintptr_t)p.W & 15u) return false;             // bulk copies need 16-byte aligned sources
   if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
+  if (p.epi == P0P_EPI_HEADS && ((uintptr_t)p.RP & 7u)) return false;      // the epilogue reads (cos, sin) as one 8-byte load
   return true;
 }
 

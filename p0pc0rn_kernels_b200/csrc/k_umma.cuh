@@ -22,6 +22,8 @@
 #pragma once
 #include <cuda.h>
 
+#include <cmath>
+
 #include "common.cuh"
 #include "ctx.h"
 #include "epilogue.cuh"
@@ -35,13 +37,16 @@ constexpr int U_NQ_MAX = 8;              // most stages of quantised records
 constexpr int U_A_BYTES = 128 * 128;     // one weight operand stage: 128 rows x 64 fp16
 constexpr int U_EPI_TB = 16;             // tokens per epilogue pass
 constexpr int U_TMEM_COLS = 512;
+constexpr int U_EPI_BYTES = 2 * U_EPI_TB * 132 * 4;   // epilogue scratch: two staging areas for the row-wise stores
 
 struct UmmaP {
   KP p;
-  uint32_t BT;          // tokens per tile (UMMA N): 16, 32, 64, 128 or 256
+  uint32_t BT;          // tokens per tile: a multiple of 16 up to 256 (one UMMA of N = BT), or of 32 up to 384 (two of N = BT / 2)
+  uint32_t NACC;        // accumulators: 2 (the next tile's multiply overlaps the epilogue) or 1 (wide tiles: tensor memory holds one)
   uint32_t NS;          // operand stages (3 or 4)
   uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
+  uint32_t G;           // token tiles per group of the tile order (tile_coords)
   int* status;
 };
 
@@ -58,6 +63,15 @@ __device__ __forceinline__ uint4 u_lds128(uint32_t a) { uint4 v; asm volatile("l
 __device__ __forceinline__ uint32_t u_lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint16_t u_lds16(uint32_t a) { uint16_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory"); return v; }
 
+// Tile order.  The blocks that run together should re-read as little as possible: a group of G token tiles is walked
+// column tile by column tile (the G blocks of one column tile share its weights), group after group.  G = m_tiles is
+// column-major order (weights stream once, every token tile is re-read per column tile: right when the tokens fit
+// the L2), G = 1 the opposite; launch_umma picks G from the two tile sizes.
+__device__ __forceinline__ void tile_coords(const UmmaP& u, uint32_t tile, uint32_t& nt, uint32_t& mt) {
+  const uint32_t per = u.G * u.n_tiles, g = tile / per, local = tile - g * per, gsz = min(u.G, u.m_tiles - g * u.G);
+  nt = local / gsz; mt = g * u.G + (local - nt * gsz);
+}
+
 // ring position that wraps without division
 struct Ring {
   uint32_t s = 0, ph = 0, n;
@@ -67,20 +81,25 @@ struct Ring {
 
 // ATM: the dequantised weight operand lives in tensor memory (written with tcgen05.st) instead of shared memory.
 // Shared-memory bandwidth is what bounds the kernel otherwise: per 64-k step a 128 x 64 fp16 tile would be
-// written once and read once there, on top of the token tile and the records.  Tensor memory then holds two
-// accumulators of up to 192 columns and four 32-column operand stages (2 x 192 + 4 x 32 = 512).
+// written once and read once there, on top of the token tile and the records.  Tensor memory then holds 384
+// accumulator columns and four 32-column operand stages (384 + 4 x 32 = 512).  The accumulator columns are two
+// tiles of up to 192 tokens (the next tile's multiply overlaps the epilogue) or ONE tile of up to 384 tokens: the
+// dequantisation of a weight block costs the same whatever the tile's width, so a wide tile halves that cost per
+// token, which is worth more than the overlap whenever M gives the wide tile enough tokens.
 constexpr uint32_t U_ACC_STRIDE_ATM = 192, U_A_COL0_ATM = 384;
 template <int ENC, bool ATM>
 __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW) {
   extern __shared__ unsigned char smem_raw[];
   const KP& p = u.p;
   const uint32_t BT = u.BT, NS = u.NS, NQ = u.NQ;
+  const uint32_t HB = BT > 256u ? BT / 2u : BT, NH = BT > 256u ? 2u : 1u;          // tokens per UMMA / TMA box, and how many of them make a tile
+  const bool two_acc = u.NACC == 2u;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                     // operand tiles need 1024-byte alignment
   unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * BT * 128u;
   const uint32_t acc_stride = ATM ? U_ACC_STRIDE_ATM : 256u;
   const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * UQ<ENC>::STAGE);
-  const uint32_t bars = epi_sh + U_EPI_TB * 132u * 4u;
+  const uint32_t bars = epi_sh + (uint32_t)U_EPI_BYTES;
   float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
   // barrier slots (8 bytes each): operands of a stage ready / stage free / record stage ready / record stage free / accumulator ready / free
   const uint32_t full = bars, empty = full + 8u * 4u, wq_full = empty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ_MAX;
@@ -111,11 +130,11 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       Ring r(NS);
       bool ok = true;
       for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles;
+        uint32_t nt, mt; tile_coords(u, tile, nt, mt);
         for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
           if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
           mbar_expect_tx(full + 8u * r.s, BT * 128u + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u));
-          tma_load_2d(x_st + r.s * BT * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT), full + 8u * r.s);
+          for (uint32_t h = 0; h < NH; h++) tma_load_2d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT + h * HB), full + 8u * r.s);
           if (ENC == P0P_ENC_F16) tma_load_2d(a_st + r.s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), full + 8u * r.s);
         }
       }
@@ -128,7 +147,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       bool ok = true;
       const uint32_t last = (p.Nw >> 6) - 1u;                  // record tiles past the weight's end do not exist: their columns are never stored
       for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const uint32_t nt = tile / u.m_tiles;
+        uint32_t nt, mt; tile_coords(u, tile, nt, mt);
         uint32_t trow[2];
         if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
         else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
@@ -144,52 +163,63 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       }
     }
   } else if (warp == 1) {
-    // ================================================================= MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(128u, BT);
-      Ring r(NS);
-      uint32_t tl = 0;
-      bool ok = true;
-      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, tl++) {
-        const uint32_t buf = tl & 1u;
-        if (!mbar_wait(acc_empty + 8u * buf, ((tl >> 1) & 1u) ^ 1u, u.status, 203, 100u)) { ok = false; break; }
+    // ================================================================= MMA issuer.  The WHOLE warp walks the loop and one
+    // elected lane issues: in warp-uniform control flow the descriptors live in uniform registers, which is what the
+    // instruction takes; inside a one-lane branch every operand of every tcgen05.mma is first moved there, which
+    // costs more than the multiply itself.
+    const uint32_t idesc = umma_idesc_f16(128u, HB);
+    Ring r(NS);
+    uint32_t tl = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, tl++) {
+      const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8u * buf, par ^ 1u, u.status, 203, 100u))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * acc_stride;
+      for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
+        if (!__all_sync(0xffffffffu, mbar_wait(full + 8u * r.s, r.ph, u.status, 204))) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * acc_stride;
-        for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
-          if (!mbar_wait(full + 8u * r.s, r.ph, u.status, 204)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t bd = umma_desc_sw128(x_st + r.s * BT * 128u);
-          if (ATM) {
-            const uint32_t at = tmem_base + U_A_COL0_ATM + r.s * 32u;
+        const uint64_t bd = umma_desc_sw128(x_st + r.s * BT * 128u);
+        const uint32_t at = tmem_base + U_A_COL0_ATM + r.s * 32u;
+        const uint64_t ad = umma_desc_sw128(a_st + r.s * U_A_BYTES);
+        const uint32_t first = ks;                                  // 0 on the tile's first k-step: the first multiply overwrites
+        if (elect_one()) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ts(d_tmem, at + 8u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);          // 8 columns / +32 bytes per 16 k
-          } else {
-            const uint64_t ad = umma_desc_sw128(a_st + r.s * U_A_BYTES);
-#pragma unroll
-            for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, (ks | kk) != 0u);   // +32 bytes (>>4) per 16 k
+          for (uint32_t kk = 0; kk < 4u; kk++) {                      // per 16 k: 8 tensor-memory columns / +32 bytes
+            if (ATM) {
+              umma_f16_ts(d_tmem, at + 8u * kk, bd + 2u * kk, idesc, first | kk);
+              if (NH == 2u) umma_f16_ts(d_tmem + HB, at + 8u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, first | kk);
+            } else umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, first | kk);
           }
           umma_commit(empty + 8u * r.s);
         }
-        if (ok) umma_commit(acc_full + 8u * buf);
+        __syncwarp();
       }
+      if (ok && elect_one()) umma_commit(acc_full + 8u * buf);
+      __syncwarp();
     }
   } else if (warp < 6) {
     // ================================================================= epilogue (TMEM lanes 32*(warp%4) .. +31)
     const uint32_t q = warp & 3u, c = q * 32u + lane;
-    uint32_t tl = 0;
+    uint32_t tl = 0, pass = 0;
     bool ok = true;
+    const bool vec = epilogue_vec_ok(p);
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, tl++) {
-      const uint32_t nt = tile / u.m_tiles, mt = tile % u.m_tiles, buf = tl & 1u;
-      if (ok && !mbar_wait(acc_full + 8u * buf, (tl >> 1) & 1u, u.status, 206, 1000u)) ok = false;
+      uint32_t nt, mt; tile_coords(u, tile, nt, mt);
+      const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
+      if (ok && !mbar_wait(acc_full + 8u * buf, par, u.status, 206, 1000u)) ok = false;
       tc_fence_after();
       const uint32_t m0 = mt * BT, nchunks = min(BT, p.M - m0 + (U_EPI_TB - 1u)) / U_EPI_TB;
-      for (uint32_t ch = 0; ch < nchunks; ch++) {           // uniform over the four warps: the epilogue's named barrier needs all 128 threads
-        uint32_t r[16];
+      const uint32_t t0 = tmem_base + ((q * 32u) << 16) + buf * acc_stride;
+      uint32_t r[16];
+      tmem_ld16(t0, r);                                      // (tensor memory stays allocated after a time-out: the load is safe, its result unused)
+      for (uint32_t ch = 0; ch < nchunks; ch++, pass++) {   // uniform over the four warps: the epilogue's named barrier needs all 128 threads
         float acc[U_EPI_TB];
-        if (ok) { tmem_ld16(tmem_base + ((q * 32u) << 16) + buf * acc_stride + ch * U_EPI_TB, r); tmem_ld_wait(); }
+        tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < U_EPI_TB; j++) acc[j] = ok ? __uint_as_float(r[j]) : 0.0f;
-        epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2);
+        if (ch + 1u < nchunks) tmem_ld16(t0 + (ch + 1u) * U_EPI_TB, r);      // the next pass's accumulators load behind this pass's work
+        epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
       }
       tc_fence_before();
       __syncwarp();
@@ -210,31 +240,39 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       for (uint32_t ks = 0; ks < KS; ks++) {
         const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == KS - 1u;
         if (turn == grp) {
-          if (!mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
+          // the record stage is awaited at this group's first use of it only (sub 0 or 1: the groups alternate)
+          if ((sub < 2u && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
           const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + sub * UQ<ENC>::RB;
           const uint32_t dst = a_st + ar.s * U_A_BYTES + r * 128u;
           if (ENC == P0P_ENC_Q4) {
+            // both 32-k halves of the row are fetched first and share ONE exactness vote: a vote and a branch per half
+            // would expose the shared-memory latency twice and end the scheduler's view between the halves
+            const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 1280u);
+            const uint32_t sm0 = u_lds32(rec + rec_sm), sm1 = u_lds32(rec + rec_sm + 1280u);
+            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            __half2 v[32];
+            if (__all_sync(0xffffffffu, q4_pair_exact(sm0) && q4_pair_exact(sm1))) {
+              const __half2 s20 = __half2half2(__ushort_as_half((unsigned short)(sm0 & 0xffffu))), m20 = __half2half2(__ushort_as_half((unsigned short)(sm0 >> 16)));
+              const __half2 s21 = __half2half2(__ushort_as_half((unsigned short)(sm1 & 0xffffu))), m21 = __half2half2(__ushort_as_half((unsigned short)(sm1 >> 16)));
 #pragma unroll
-            for (uint32_t kh = 0; kh < 2u; kh++) {
-              __half2 v[16];
-              const uint4 cq = u_lds128(rec + rec_row + kh * 1280u);
-              const uint32_t sm = u_lds32(rec + rec_sm + kh * 1280u);
-              const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
-              if (__all_sync(0xffffffffu, q4_pair_exact(sm))) {
-                const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+              for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s20, m20, v + 4 * i);
 #pragma unroll
-                for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
-              } else {
+              for (int i = 4; i < 8; i++) q4_word_to_half2x4(w[i], s21, m21, v + 4 * i);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i++) {
+                const uint32_t sm = i < 16 ? sm0 : sm1;
                 const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
-#pragma unroll
-                for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+                v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
               }
-              if (ATM) {
-                tmem_st16(tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM + ar.s * 32u + kh * 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
-              } else {
+            }
+            if (ATM) {
+              const uint32_t ta = tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM + ar.s * 32u;
+              tmem_st16(ta, *reinterpret_cast<const uint32_t(*)[16]>(v));
+              tmem_st16(ta + 16u, *reinterpret_cast<const uint32_t(*)[16]>(v + 16));
+            } else {
 #pragma unroll
-                for (uint32_t j = 0; j < 4u; j++) sts128(dst + (((kh * 4u + j) ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[j]);
-              }
+              for (uint32_t j = 0; j < 8u; j++) sts128(dst + ((j ^ rsw) << 4), reinterpret_cast<const uint4*>(v)[j]);
             }
           } else {
             const __half2 s2 = __half2half2(__ushort_as_half(u_lds16(rec + rec_sm)));
@@ -326,6 +364,7 @@ inline bool umma_supported(const p0p_ctx*, const KP& p) {
   if (p.xmode == P0P_X_F16 && !p.vecx) return false;
   if ((p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD) && (((uintptr_t)p.X & 15u) || p.ldx % 4u || p.kx0 % 4u)) return false;
   if ((uintptr_t)p.W & 15u) return false;
+  if (p.epi == P0P_EPI_HEADS && ((uintptr_t)p.RP & 7u)) return false;      // the epilogue reads (cos, sin) as one 8-byte load
   if (p.enc == P0P_ENC_F16) {
     if (!p.vecw || p.epi == P0P_EPI_SWIGLU) return false;
   } else {
@@ -352,38 +391,47 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
     c->launches += 1;
     xbase = c->scratch; xld = p.K;
   } else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
-  // ---- tile shape.  Quantised weights: operand in tensor memory, up to 192 tokens per tile; fp16 weights: both
-  // operands in shared memory, up to 256.  Within that, the width that leaves the fewest idle SM-rounds.
+  // ---- tile shape.  fp16 weights: both operands in shared memory, up to 256 tokens, two accumulators.  Quantised
+  // weights (operand in tensor memory): up to 192 tokens with two accumulators, or up to 384 with one.  A k-step of
+  // a tile costs max(2 * tokens, ~1000) cycles (tensor pipe against the dequantisation of the 128 x 64 weight block),
+  // a single-accumulator tile also exposes its epilogue (~24 cycles per token); the cheapest total wins.
   const bool atm = p.enc != P0P_ENC_F16;
   const uint32_t ncols = (p.epi == P0P_EPI_SWIGLU || p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u);
   u.n_tiles = (ncols + 127u) / 128u;
-  const uint32_t bt_max = atm ? 192u : 256u;
+  const uint32_t bt_max = atm ? 384u : 256u, KSn = p.K / 64u;
   uint32_t BT;
-  if (p.M <= bt_max) BT = std::max(16u, (p.M + 15u) & ~15u);
+  if (p.M <= 256u) BT = std::max(16u, (p.M + 15u) & ~15u);
   else {
-    uint64_t best = ~0ull; BT = bt_max;
+    uint64_t best = ~0ull; BT = 0;
     for (uint32_t cand = bt_max; cand >= 128u; cand -= 16u) {
-      // a k-step costs about the same for any width up to ~320 tokens (the dequantisation bounds it), so fewer rounds win
-      const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand), cost = ((t + sms - 1) / sms) * std::max(cand, atm ? 320u : 192u);
-      if (cost < best) { best = cost; BT = cand; }
+      if (cand > 256u && cand % 32u) continue;
+      const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand), rounds = (t + sms - 1) / sms;
+      const uint64_t per_tile = (uint64_t)KSn * std::max<uint64_t>(2u * cand, atm ? 1000u : 384u) + ((atm && cand > 192u) ? 24u * cand : 0u);
+      if (rounds * per_tile < best) { best = rounds * per_tile; BT = cand; }
     }
   }
-  u.BT = BT; u.NS = (!atm && BT > 192u) ? 3u : 4u;
+  u.BT = BT; u.NACC = (atm && BT > 192u) ? 1u : 2u;
+  u.NS = (BT > 256u || (!atm && BT > 192u)) ? 3u : 4u;
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
-  const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + U_EPI_TB * 132u * 4u + 512u;
+  const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + (size_t)U_EPI_BYTES + 512u;
   u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (100 * 1024 + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
   if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
   u.m_tiles = (p.M + BT - 1u) / BT;
+  {   // a wave of `sms` tiles reads G token tiles and sms / G weight tiles: least bytes at G = sqrt(sms * weight tile / token tile)
+    const double wt = 128.0 * (p.enc == P0P_ENC_Q4 ? 0.625 : p.enc == P0P_ENC_Q8 ? 1.03125 : 2.0), xt = 2.0 * BT;
+    const double g = std::sqrt((double)sms * wt / xt);
+    u.G = (uint32_t)std::min<double>(std::max(1.0, std::floor(g + 0.5)), (double)u.m_tiles);
+  }
   u.p = p; u.status = c->dev_status;
   CUtensorMap mx, mw;
-  if (!make_map(&mx, xbase, p.K, p.M, xld, BT)) return fail(c, -12, "gemm: the token tensor map could not be encoded");
+  if (!make_map(&mx, xbase, p.K, p.M, xld, BT > 256u ? BT / 2u : BT)) return fail(c, -12, "gemm: the token tensor map could not be encoded");
   if (p.enc == P0P_ENC_F16) {
     if (!make_map(&mw, reinterpret_cast<const __half*>(p.W) + p.wk0, p.K, p.Nw, p.wG, 128u)) return fail(c, -12, "gemm: the weight tensor map could not be encoded");
   } else mw = mx;
   const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
-  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + U_EPI_TB * 132u * 4u + 512u);
+  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 512u);
   const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles, sms);
   const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);

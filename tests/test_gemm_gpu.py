@@ -246,6 +246,9 @@ UMMA = [
     dict(name="u q8 M520 3 token tiles", enc="q8", M=520, N=256, K=1024),
     dict(name="u f16 M200 ld", enc="f16", M=200, N=320, K=448, w_ld=456, w_cols=456, wr0=5, w_rows=330),
     dict(name="u q4 M17", enc="q4", M=17, N=256, K=256),
+    dict(name="u q4 M384 one wide tile, ring wrap", enc="q4", M=384, N=640, K=1280),
+    dict(name="u q8 M777 wide tiles, many", enc="q8", M=777, N=2560, K=448, epi="resadd"),
+    dict(name="u q4 M250 single accumulator, narrow", enc="q4", M=250, N=1280, K=192, epi="swiglu"),
     dict(name="u f16 M3 (small M, fp16 weights)", enc="f16", M=3, N=256, K=512),
     dict(name="u q4 many tiles (two accumulators, ring wrap)", enc="q4", M=1024, N=6144, K=320),
     dict(name="u q8 many tiles", enc="q8", M=700, N=5120, K=192),
