@@ -43,6 +43,7 @@ struct UmmaP {
   KP p;
   uint32_t BT;          // tokens per tile: a multiple of 16 up to 256 (one UMMA of N = BT), or of 32 up to 384 (two of N = BT / 2)
   uint32_t NACC;        // accumulators: 2 (the next tile's multiply overlaps the epilogue) or 1 (wide tiles: tensor memory holds one)
+  uint32_t KSPLIT;      // accumulators per tile that take the 16-k multiplies in turn (1, 2 or 4), summed by the epilogue
   uint32_t NS;          // operand stages (3 or 4)
   uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
@@ -186,10 +187,13 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         if (elect_one()) {
 #pragma unroll
           for (uint32_t kk = 0; kk < 4u; kk++) {                      // per 16 k: 8 tensor-memory columns / +32 bytes
+            // consecutive multiplies into ONE accumulator start ~180 cycles apart whatever their width; into different
+            // accumulators ~35.  Narrow tiles therefore rotate over KSPLIT accumulators (wide ones over their two halves).
+            const uint32_t dk = d_tmem + (kk & (u.KSPLIT - 1u)) * BT, accum = first | (kk >= u.KSPLIT ? 1u : 0u);
             if (ATM) {
-              umma_f16_ts(d_tmem, at + 8u * kk, bd + 2u * kk, idesc, first | kk);
-              if (NH == 2u) umma_f16_ts(d_tmem + HB, at + 8u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, first | kk);
-            } else umma_f16_ss(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, first | kk);
+              umma_f16_ts(dk, at + 8u * kk, bd + 2u * kk, idesc, accum);
+              if (NH == 2u) umma_f16_ts(dk + HB, at + 8u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
+            } else umma_f16_ss(dk, ad + 2u * kk, bd + 2u * kk, idesc, accum);
           }
           umma_commit(empty + 8u * r.s);
         }
@@ -218,6 +222,11 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < U_EPI_TB; j++) acc[j] = ok ? __uint_as_float(r[j]) : 0.0f;
+        for (uint32_t a = 1; a < u.KSPLIT; a++) {            // the tile's other accumulators (narrow tiles only: few passes)
+          tmem_ld16(t0 + a * BT + ch * U_EPI_TB, r); tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < U_EPI_TB; j++) acc[j] += ok ? __uint_as_float(r[j]) : 0.0f;
+        }
         if (ch + 1u < nchunks) tmem_ld16(t0 + (ch + 1u) * U_EPI_TB, r);      // the next pass's accumulators load behind this pass's work
         epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
       }
@@ -411,6 +420,12 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
     }
   }
   u.BT = BT; u.NACC = (atm && BT > 192u) ? 1u : 2u;
+  // accumulators per tile: as many as the accumulator columns hold (192 per buffer with the operand in tensor memory, 256
+  // without).  96 < BT <= 192 gives up the second buffer for a second accumulator when the k loop is long enough to pay
+  // for the exposed epilogue.
+  const uint32_t acc_cols = atm ? 192u : 256u;
+  u.KSPLIT = BT * 4u <= acc_cols ? 4u : BT * 2u <= acc_cols ? 2u : 1u;
+  if (atm && u.KSPLIT == 1u && BT <= 192u && KSn >= 32u) { u.KSPLIT = 2u; u.NACC = 1u; }
   u.NS = (BT > 256u || (!atm && BT > 192u)) ? 3u : 4u;
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
