@@ -97,7 +97,7 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3):
+def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3, reps=1):
     """the reference's CPU path on a bounded sample of the block: M_rows tokens, the first gu_cols hidden columns of
     the gate/up GEMM (RMS prologue, SwiGLU) and the first dn_cols output columns of the down GEMM (residual add)"""
     import oracle as O
@@ -108,14 +108,15 @@ def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3):
     Wdn, _ = O.pack_q4((rs.standard_normal(dn_cols * FF) * 0.02).astype(np.float32), dn_cols, FF)
     Hfull = O.to_f16(rs.standard_normal(M_rows * FF).astype(np.float32))
     t0 = time.perf_counter()
-    ST = O.rowstats(X, M_rows, HID, rms=True)
-    Hh = np.zeros(M_rows * gu_cols, np.uint16)
-    O.gemm(enc="q4g32a.t64", X=X, W=Wgu, Y=Hh, M=M_rows, N=2 * gu_cols, K=HID, w_rows=2 * gu_cols, w_cols=HID, xmode="rms", epi="swiglu",
-           wr0=0, wr1=gu_cols, ldy=gu_cols, ST=ST, PV=gamma, threads=threads)
-    R = X[: M_rows * HID].reshape(M_rows, HID)[:, :dn_cols].copy()
-    O.gemm(enc="q4g32a.t64", X=Hfull, W=Wdn, Y=R, M=M_rows, N=dn_cols, K=FF, w_rows=dn_cols, w_cols=FF, epi="resadd", threads=threads)
+    for _ in range(reps):
+        ST = O.rowstats(X, M_rows, HID, rms=True)
+        Hh = np.zeros(M_rows * gu_cols, np.uint16)
+        O.gemm(enc="q4g32a.t64", X=X, W=Wgu, Y=Hh, M=M_rows, N=2 * gu_cols, K=HID, w_rows=2 * gu_cols, w_cols=HID, xmode="rms", epi="swiglu",
+               wr0=0, wr1=gu_cols, ldy=gu_cols, ST=ST, PV=gamma, threads=threads)
+        R = X[: M_rows * HID].reshape(M_rows, HID)[:, :dn_cols].copy()
+        O.gemm(enc="q4g32a.t64", X=Hfull, W=Wdn, Y=R, M=M_rows, N=dn_cols, K=FF, w_rows=dn_cols, w_cols=FF, epi="resadd", threads=threads)
     dt = time.perf_counter() - t0
-    fl = 2.0 * M_rows * (2 * gu_cols) * HID + 2.0 * M_rows * dn_cols * FF
+    fl = reps * (2.0 * M_rows * (2 * gu_cols) * HID + 2.0 * M_rows * dn_cols * FF)
     return fl, dt
 
 
@@ -191,6 +192,103 @@ def run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world):
     os._exit(0)
 
 
+def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
+    """The two other single-GPU configurations of the baseline, one JSON line each:
+    dit_qkv  q8 projection of 3600 tokens, hidden 3072 -> 9216 with the LayerNorm + modulation prologue and the QK-norm + RoPE
+             head-split epilogue (24 + 24 + 24 heads of 128);
+    conv3    3x3x3 convolution of a 13 x 92 x 160 x 128 clip to 128 channels (fp16 weights in the converter's layout, bias),
+             run whole and as 4-frame chunks out of a ring of 6 frames; the two outputs must be bit-identical."""
+    rs = np.random.default_rng(11)
+
+    def graph_time(fn, reps):
+        fn(); fn(); torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream): fn()
+        for _ in range(3): g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps): g.replay()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for name in args.config.split(","):
+        if name == "dit_qkv":
+            M, K, N, H = 3600, 3072, 9216, 24
+            x = gpu.upload(rs.standard_normal(M * K).astype(np.float32)); st = gpu.buffer(M * 8)
+            pv = gpu.upload(P.fromF16(P.toF16((rs.standard_normal(2 * K) * 0.5).astype(np.float32))))        # scale | shift, fp16-rounded values held as f32
+            slab = P.packQ8((rs.standard_normal(1024 * K) * 0.02).astype(np.float32), 1024, K)
+            wbytes = np.tile(slab, N // 1024)
+            Ws = [gpu.upload(wbytes) for _ in range(5)]                                                      # 5 x 29 MB > L2
+            ev = gpu.upload((1 + 0.1 * rs.standard_normal(256)).astype(np.float32))
+            ang = rs.uniform(0, 6.28, M * 64).astype(np.float32)
+            rp = gpu.upload(np.stack([np.cos(ang), np.sin(ang)], -1).astype(np.float32).ravel())
+            y = gpu.buffer(3 * H * M * 128 * 2)
+            P.rowstats(gpu, {"x": {"buf": x}, "rows": M, "cols": K, "mode": "ln", "eps": 1e-6, "st": {"buf": st}})
+            i = [0]
+            def call():
+                i[0] = (i[0] + 1) % len(Ws)
+                a = {"w": {"enc": "q8g64s.t64", "buf": Ws[i[0]], "off": 0, "bytes": wbytes.nbytes, "rows": N, "cols": K}, "x": {"buf": x, "mode": "lnmod"},
+                     "y": {"buf": y}, "M": M, "N": N, "K": K, "epi": "heads", "stats": {"buf": st}, "pv": {"buf": pv, "off": 0, "stride": K}, "ev": {"buf": ev},
+                     "heads": {"Ltot": M, "Hq": H, "Hkv": H, "rowOff": 0, "eps": 1e-6, "rope": {"buf": rp}}}
+                if args.kernel: a["kernel"] = args.kernel
+                P.gemm(gpu, a)
+            # one graph per weight copy would need five graphs; the kernel is 0.2 ms, so eager launches on the stream are timed instead
+            for _ in range(5): call()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(args.steps, 10)
+            e0.record()
+            for _ in range(reps): call()
+            e1.record(); torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            fl = 2.0 * M * N * K; by = wbytes.nbytes + M * K * 4 + M * N * 2 + M * 8 + 2 * K * 4 + M * 128 * 4
+            print(json.dumps({"config": "dit_qkv (configs[2])", "family": P._lib.KERNEL_NAMES.get(gpu.lastKernel), "M": M, "N": N, "K": K, "ms": ms,
+                              "TFLOP/s": fl / (ms * 1e-3) / 1e12, "GB/s": by / (ms * 1e-3) / 1e9, "frac_tensor": fl / (ms * 1e-3) / 1e12 / pk["tensor"]}), flush=True)
+            for b in Ws + [x, st, pv, ev, rp, y]: gpu.free(b)
+            gpu.drainPool()
+        elif name == "conv3":
+            T, Hh, Ww, C, N = 13, 92, 160, 128, 128
+            K = 27 * C; fx = Hh * Ww * C; fy = Hh * Ww * N
+            clip_t = (torch.randn(T * fx, device=dev, dtype=torch.float32)).to(torch.float16)
+            clip = gpu.wrap(clip_t.data_ptr(), clip_t.numel() * 2)
+            w5 = (rs.standard_normal(N * C * 27) * 0.03).astype(np.float32)                                   # [N][C][3][3][3] as a checkpoint holds it
+            wk = P.reorderConvRows(w5, N, [N, C, 3, 3, 3])                                                              # -> [N][(kt ky kx) C], the kernel's layout
+            wb = gpu.upload(P.toF16(wk)); bias = gpu.upload((rs.standard_normal(N) * 0.1).astype(np.float32))
+            ya_t = torch.zeros(T * fy, device=dev, dtype=torch.float16); yb_t = torch.zeros(T * fy, device=dev, dtype=torch.float16)
+            ya, yb = gpu.wrap(ya_t.data_ptr(), T * fy * 2), gpu.wrap(yb_t.data_ptr(), T * fy * 2)
+            ring_t = torch.zeros(6 * fx, device=dev, dtype=torch.float16); ring = gpu.wrap(ring_t.data_ptr(), 6 * fx * 2)
+
+            def conv(xbuf, xoff, ybuf, yoff, t0, nf, padL, ks):
+                a = {"w": {"enc": "f16", "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": {"buf": xbuf, "off": xoff}, "y": {"buf": ybuf, "off": yoff},
+                     "M": nf * Hh * Ww, "N": N, "K": K, "epi": "bias", "ev": {"buf": bias},
+                     "conv": {"kind": "conv3", "Hi": Hh, "Wi": Ww, "Ci": C, "Ho": Hh, "Wo": Ww, "stride": T, "padT": t0, "padL": padL, "ks": ks}}
+                if args.kernel: a["kernel"] = args.kernel
+                P.gemm(gpu, a)
+
+            def whole(): conv(clip, 0, ya, 0, 0, T, 0, 1)
+            def chunks():
+                have = set()
+                for t0 in range(0, T, 4):
+                    nf = min(4, T - t0)
+                    for g in range(max(0, t0 - 1), min(T - 1, t0 + nf) + 1):                                   # frames t0-1 .. t0+nf into their ring slots
+                        if g not in have:
+                            ring_t[(g % 6) * fx:(g % 6 + 1) * fx].copy_(clip_t[g * fx:(g + 1) * fx]); have.add(g)
+                    conv(ring, 0, yb, t0 * fy * 2, t0, nf, 0, 6)
+            reps = max(3, min(args.steps, 20))
+            ms_w = graph_time(whole, reps); fam = P._lib.KERNEL_NAMES.get(gpu.lastKernel)
+            ms_c = graph_time(chunks, reps)
+            torch.cuda.synchronize()
+            same = bool(torch.equal(ya_t.view(torch.int16), yb_t.view(torch.int16)))
+            fl = 2.0 * T * Hh * Ww * N * K; by = T * fx * 2 + N * K * 2 + T * fy * 2 + N * 4
+            print(json.dumps({"config": "conv3 (configs[3])", "family": fam, "M": T * Hh * Ww, "N": N, "K": K, "ms_whole": ms_w, "ms_chunks_of_4_from_ring_of_6": ms_c,
+                              "TFLOP/s_whole": fl / (ms_w * 1e-3) / 1e12, "TFLOP/s_chunks": fl / (ms_c * 1e-3) / 1e12, "GB/s_whole": by / (ms_w * 1e-3) / 1e9,
+                              "frac_tensor_whole": fl / (ms_w * 1e-3) / 1e12 / pk["tensor"], "chunks_bit_identical_to_whole": same}), flush=True)
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,6 +300,7 @@ def main():
     ap.add_argument("--skip-cases", action="store_true", help="only the headline (for profiler captures)")
     ap.add_argument("--kernel", default=None, help="force a kernel family (generic | decode | umma)")
     ap.add_argument("--shape", default=None, help="enc:M:N:K[,enc:M:N:K...]  time plain GEMMs of these shapes instead of the block (q4|q8|f16)")
+    ap.add_argument("--config", default=None, help="dit_qkv | conv3 [,…]: time the baseline's other single-GPU configurations instead of the block")
     ap.add_argument("--sweep", action="store_true", help="the large-shape sweep of the baseline's configs (q4/q8, M in 1..8192, four (N,K))")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local = int(os.environ.get("LOCAL_RANK", 0))
@@ -225,6 +324,8 @@ def main():
 
     if args.shape or args.sweep:
         return run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world)
+    if args.config:
+        return run_configs(args, P, torch, gpu, stream, dev, pk, rank, world)
 
     # ---- model state: this rank's column shard of both weights (the whole weights at N = 1), `copies` times
     ffl, hidl = FF // world, HID // world
@@ -401,9 +502,9 @@ def main():
         O.build(); thr = O.max_threads()
         cpu_sample(1, 256, 128, thr)
         cm = min(M, 512)
-        f, d = cpu_sample(cm, 4096, 2048, thr)
+        f, d = cpu_sample(cm, FF // 2, HID // 2, thr, reps=4)
         cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port",
-               "sample": f"{cm} tokens x 4096 of {FF} hidden columns (gate/up) + 2048 of {HID} output columns (down), float64 accumulate, {d:.1f} s"}
+               "sample": f"{cm} tokens x {FF // 2} of {FF} hidden columns (gate/up) + {HID // 2} of {HID} output columns (down), 4 passes, float64 accumulate, {d:.1f} s"}
         out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (q4 weights dequantised in-kernel)",
                "data": "synthetic",

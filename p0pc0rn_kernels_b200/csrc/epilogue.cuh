@@ -74,26 +74,59 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
   const uint32_t col = nB + c, epi = p.epi, lane = c & 31u, wq = c >> 5;
   __half* Yh = reinterpret_cast<__half*>(p.Y); float* Yf = reinterpret_cast<float*>(p.Y);
   if (epi == P0P_EPI_HEADS || epi == P0P_EPI_ONORMGATE) {
-    // ---- sum of squares over the 128 columns, per token
-    float* part = sh;                 // [4][TB]
+    float* part = sh;                 // [4][TB] sums of squares per warp
     float* xch = sh + 4 * TB;         // [TB][128] partner exchange for the (d, d+64) rotation
-#pragma unroll
-    for (int j = 0; j < TB; j++) {
-      float s = acc[j] * acc[j];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0) part[wq * TB + j] = s;
-    }
-    bar_sync_named(barid, 128);
     const bool half_mode = epi == P0P_EPI_HEADS && (p.flags & P0P_F_ROPE_HALF);
     const uint32_t hd = nB / 128u, sec = epi == P0P_EPI_ONORMGATE ? 0u : (hd < p.Hq ? 0u : hd < p.Hq + p.Hkv ? 1u : 2u);
-    const float nw = (epi == P0P_EPI_ONORMGATE || sec < 2u) ? __ldg(p.EV + p.evOff + (sec == 1u ? 128u : 0u) + c) : 1.0f;
     float v[TB];
+    if (sec < 2u) {                   // Q, K (and onormgate): RMS norm over the block's 128 columns; V heads pass through
+      // ---- sum of squares over the 128 columns, per token
+      if (TB == 16) {
+        // transposing reduction: at each step a lane hands half of its tokens to its partner and keeps the other half, so 16
+        // shuffles (instead of 80) leave every lane pair with one token's sum over the warp's 32 columns
+        float s[16];
 #pragma unroll
-    for (int j = 0; j < TB; j++) {
-      const float ss = part[j] + part[TB + j] + part[2 * TB + j] + part[3 * TB + j];
-      const float inv = rsqrtf(ss / 128.0f + p.eps);
-      v[j] = (epi == P0P_EPI_ONORMGATE || sec < 2u) ? acc[j] * inv * nw : acc[j];
+        for (int j = 0; j < 16; j++) s[j] = acc[j % TB] * acc[j % TB];
+#pragma unroll
+        for (int w = 8; w >= 1; w >>= 1) {                       // w tokens kept per lane after the step with partner lane ^ (2 w)
+          const bool up = (lane & (2u * w)) != 0u;
+#pragma unroll
+          for (int i = 0; i < w; i++) {
+            const float send = up ? s[i] : s[i + w], keep = up ? s[i + w] : s[i];
+            s[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2 * w);
+          }
+        }
+        s[0] += __shfl_xor_sync(0xffffffffu, s[0], 1);
+        const uint32_t t = ((lane >> 4) & 1u) * 8u + ((lane >> 3) & 1u) * 4u + ((lane >> 2) & 1u) * 2u + ((lane >> 1) & 1u);
+        if (!(lane & 1u)) part[wq * TB + t] = s[0];
+      } else {
+#pragma unroll
+        for (int j = 0; j < TB; j++) {
+          float s = acc[j] * acc[j];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (lane == 0) part[wq * TB + j] = s;
+        }
+      }
+      bar_sync_named(barid, 128);
+      const float nw = __ldg(p.EV + p.evOff + (sec == 1u ? 128u : 0u) + c);
+      if (TB % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < TB; j += 4) {
+          const float4 a0 = *reinterpret_cast<const float4*>(part + j), a1 = *reinterpret_cast<const float4*>(part + TB + j);
+          const float4 a2 = *reinterpret_cast<const float4*>(part + 2 * TB + j), a3 = *reinterpret_cast<const float4*>(part + 3 * TB + j);
+          v[j] = acc[j] * rsqrtf((a0.x + a1.x + a2.x + a3.x) / 128.0f + p.eps) * nw;
+          v[j + 1] = acc[j + 1] * rsqrtf((a0.y + a1.y + a2.y + a3.y) / 128.0f + p.eps) * nw;
+          v[j + 2] = acc[j + 2] * rsqrtf((a0.z + a1.z + a2.z + a3.z) / 128.0f + p.eps) * nw;
+          v[j + 3] = acc[j + 3] * rsqrtf((a0.w + a1.w + a2.w + a3.w) / 128.0f + p.eps) * nw;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < TB; j++) v[j] = acc[j] * rsqrtf((part[j] + part[TB + j] + part[2 * TB + j] + part[3 * TB + j]) / 128.0f + p.eps) * nw;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < TB; j++) v[j] = acc[j];
     }
     if (epi == P0P_EPI_ONORMGATE) {
 #pragma unroll

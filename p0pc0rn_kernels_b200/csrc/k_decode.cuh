@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 // ---- stage 2: fixed-order sum over the k-blocks, then the fused epilogue.  One block per 128 output columns.
 template <int MP>
 __global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
-  __shared__ float sh[MP * 132];
+  __shared__ __align__(16) float sh[MP * 132];
   const KP& p = d.p;
   const uint32_t c = threadIdx.x, nB = blockIdx.x * 128u, col = nB + c;
   uint32_t slot;

@@ -48,6 +48,7 @@ struct UmmaP {
   uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
   uint32_t G;           // token tiles per group of the tile order (tile_coords)
+  uint32_t cvR;         // conv3: image rows per token tile (tile = cvR x Wo output positions of one frame)
   int* status;
 };
 
@@ -135,7 +136,19 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
           if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
           mbar_expect_tx(full + 8u * r.s, BT * 128u + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u));
-          for (uint32_t h = 0; h < NH; h++) tma_load_2d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT + h * HB), full + 8u * r.s);
+          if (p.xmode == P0P_X_CONV3) {
+            // implicit GEMM (src/ops/gemm.js:68-80): the 64 k of this step are channels c0.. of ONE tap (kt, ky, kx); the tile's
+            // tokens are cvR whole rows of one output frame, so their inputs are a box of the clip shifted by the tap, and
+            // what falls outside the image reads as zero.  Frame index: clamp to the clip, then ring slot or chunk offset.
+            const uint32_t tpf = p.Ho / u.cvR, ot = mt / tpf, oy0 = (mt - ot * tpf) * u.cvR;
+            const uint32_t kg = ks * 64u, tap = kg / p.Ci, c0 = kg - tap * p.Ci, kt = tap / 9u, ky = (tap / 3u) % 3u, kx = tap % 3u;
+            const int itg = min(max((int)(ot + p.padT + kt) - 1, 0), (int)p.stride - 1);
+            const int it = p.ks > 1u ? itg % (int)p.ks : itg - (int)p.padL;
+            const uint32_t rb = u.cvR / NH;
+            for (uint32_t h = 0; h < NH; h++)
+              tma_load_4d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)c0, (int)kx - 1, (int)(oy0 + h * rb + ky) - 1, it, full + 8u * r.s);
+          } else
+            for (uint32_t h = 0; h < NH; h++) tma_load_2d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT + h * HB), full + 8u * r.s);
           if (ENC == P0P_ENC_F16) tma_load_2d(a_st + r.s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), full + 8u * r.s);
         }
       }
@@ -193,7 +206,10 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
             if (ATM) {
               umma_f16_ts(dk, at + 8u * kk, bd + 2u * kk, idesc, accum);
               if (NH == 2u) umma_f16_ts(dk + HB, at + 8u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
-            } else umma_f16_ss(dk, ad + 2u * kk, bd + 2u * kk, idesc, accum);
+            } else {
+              umma_f16_ss(dk, ad + 2u * kk, bd + 2u * kk, idesc, accum);
+              if (NH == 2u) umma_f16_ss(dk + HB, ad + 2u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
+            }
           }
           umma_commit(empty + 8u * r.s);
         }
@@ -366,10 +382,41 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t r
            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// conv3 clip [frames][Hi][Wi][Ci] fp16: box = 64 channels x Wo columns x box_rows image rows of one frame
+inline bool make_map_clip(CUtensorMap* m, const void* base, uint32_t Ci, uint32_t Wi, uint32_t Hi, uint32_t frames, uint32_t Wo, uint32_t box_rows) {
+  tmap_encode_fn f = tmap_encoder();
+  if (!f) return false;
+  const cuuint64_t dims[4] = {Ci, Wi, Hi, frames}, strides[3] = {(cuuint64_t)Ci * 2u, (cuuint64_t)Wi * Ci * 2u, (cuuint64_t)Hi * Wi * Ci * 2u};
+  const cuuint32_t box[4] = {64u, Wo, box_rows, 1u}, el[4] = {1u, 1u, 1u, 1u};
+  return f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// conv3 token tile: R whole output rows of a frame.  R depends on the image only, never on M: a clip run whole, in chunks
+// or from a ring must take the same tiles (the results are required to be bit-identical).  0 = no tile shape fits.
+inline uint32_t conv3_tile_rows(const KP& p, bool atm) {
+  if (p.Wo > 256u || p.Wo % 8u) return 0u;
+  const uint32_t bt_max = 384u;
+  for (uint32_t R = std::min(p.Ho, bt_max / p.Wo); R >= 1u; R--) {
+    const uint32_t bt = R * p.Wo;
+    if (p.Ho % R) continue;
+    if (bt <= 256u ? bt % 16u != 0u : (R % 2u != 0u || bt % 32u != 0u)) continue;
+    if (bt < 16u) continue;
+    (void)atm;
+    return R;
+  }
+  return 0u;
+}
+
 inline bool umma_supported(const p0p_ctx*, const KP& p) {
   if (!tmap_encoder()) return false;
   if (p.K % 64u) return false;
-  if (p.xmode == P0P_X_CONV || p.xmode == P0P_X_CONV3) return false;
+  if (p.xmode == P0P_X_CONV) return false;
+  if (p.xmode == P0P_X_CONV3) {
+    // one 64-k step inside one tap, plain fp16 clip (no fused PixelNorm), whole tiles of whole image rows
+    if (p.Ci % 64u || (p.flags & P0P_F_PN) || ((uintptr_t)p.X & 15u)) return false;
+    const uint32_t R = conv3_tile_rows(p, p.enc != P0P_ENC_F16);
+    if (!R || p.M % (R * p.Wo)) return false;
+  }
   if (p.xmode == P0P_X_F16 && !p.vecx) return false;
   if ((p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD) && (((uintptr_t)p.X & 15u) || p.ldx % 4u || p.kx0 % 4u)) return false;
   if ((uintptr_t)p.W & 15u) return false;
@@ -399,33 +446,41 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
     if (e != cudaSuccess) return cuda_fail(c, e, "prologue launch");
     c->launches += 1;
     xbase = c->scratch; xld = p.K;
-  } else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
+  } else if (p.xmode == P0P_X_CONV3) { xbase = p.X; xld = 0; }
+  else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
   // ---- tile shape.  fp16 weights: both operands in shared memory, up to 256 tokens, two accumulators.  Quantised
-  // weights (operand in tensor memory): up to 192 tokens with two accumulators, or up to 384 with one.  A k-step of
-  // a tile costs max(2 * tokens, ~1000) cycles (tensor pipe against the dequantisation of the 128 x 64 weight block),
-  // a single-accumulator tile also exposes its epilogue (~24 cycles per token); the cheapest total wins.
+  // weights (operand in tensor memory): up to 192 tokens with two accumulators, or up to 384 with one; the cheapest
+  // total by the cost model below wins.
   const bool atm = p.enc != P0P_ENC_F16;
   const uint32_t ncols = (p.epi == P0P_EPI_SWIGLU || p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? p.N : ((p.N + 3u) & ~3u);
   u.n_tiles = (ncols + 127u) / 128u;
   const uint32_t bt_max = atm ? 384u : 256u, KSn = p.K / 64u;
   uint32_t BT;
-  if (p.M <= 256u) BT = std::max(16u, (p.M + 15u) & ~15u);
+  if (p.xmode == P0P_X_CONV3) { u.cvR = conv3_tile_rows(p, atm); BT = u.cvR * p.Wo; }
+  else if (p.M <= 256u) BT = std::max(16u, (p.M + 15u) & ~15u);
   else {
     uint64_t best = ~0ull; BT = 0;
     for (uint32_t cand = bt_max; cand >= 128u; cand -= 16u) {
       if (cand > 256u && cand % 32u) continue;
       const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand), rounds = (t + sms - 1) / sms;
-      const uint64_t per_tile = (uint64_t)KSn * std::max<uint64_t>(2u * cand, atm ? 1000u : 384u) + ((atm && cand > 192u) ? 24u * cand : 0u);
+      // measured: a k-step costs ~750 cycles up to 256 tokens (four dependent multiplies, or the dequantisation) and
+      // ~2.5 cycles per token beyond; a single-accumulator tile exposes its epilogue, whose cost per token depends on the kind
+      const uint64_t kstep = std::max<uint64_t>(5u * cand / 2u, atm ? 750u : 720u);
+      const uint64_t epi_tok = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? 150u : p.epi == P0P_EPI_SWIGLU ? 30u : 24u;
+      // (with two accumulators the epilogue hides behind the next tile's k loop unless it is the longer of the two; it runs
+      // about half as fast there, sharing the issue slots with the dequantisation)
+      const uint64_t per_tile = (atm && cand > 192u) ? (uint64_t)KSn * kstep + epi_tok * cand : std::max<uint64_t>((uint64_t)KSn * kstep, 2u * epi_tok * cand);
       if (rounds * per_tile < best) { best = rounds * per_tile; BT = cand; }
     }
   }
-  u.BT = BT; u.NACC = (atm && BT > 192u) ? 1u : 2u;
+  u.BT = BT; u.NACC = (BT > (atm ? 192u : 256u)) ? 1u : 2u;
   // accumulators per tile: as many as the accumulator columns hold (192 per buffer with the operand in tensor memory, 256
   // without).  96 < BT <= 192 gives up the second buffer for a second accumulator when the k loop is long enough to pay
   // for the exposed epilogue.
   const uint32_t acc_cols = atm ? 192u : 256u;
   u.KSPLIT = BT * 4u <= acc_cols ? 4u : BT * 2u <= acc_cols ? 2u : 1u;
-  if (atm && u.KSPLIT == 1u && BT <= 192u && KSn >= 32u) { u.KSPLIT = 2u; u.NACC = 1u; }
+  if (atm && u.KSPLIT == 1u && BT <= 192u && KSn >= 32u && p.xmode != P0P_X_CONV3) { u.KSPLIT = 2u; u.NACC = 1u; }
+  if (p.xmode == P0P_X_CONV3) u.KSPLIT = 1u;      // one accumulation order for every call on the same clip
   u.NS = (BT > 256u || (!atm && BT > 192u)) ? 3u : 4u;
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
@@ -440,7 +495,10 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   }
   u.p = p; u.status = c->dev_status;
   CUtensorMap mx, mw;
-  if (!make_map(&mx, xbase, p.K, p.M, xld, BT > 256u ? BT / 2u : BT)) return fail(c, -12, "gemm: the token tensor map could not be encoded");
+  if (p.xmode == P0P_X_CONV3) {
+    const uint32_t frames = p.ks > 1u ? p.ks : p.stride - p.padL;
+    if (!make_map_clip(&mx, xbase, p.Ci, p.Wi, p.Hi, frames, p.Wo, BT > 256u ? u.cvR / 2u : u.cvR)) return fail(c, -12, "gemm: the clip tensor map could not be encoded");
+  } else if (!make_map(&mx, xbase, p.K, p.M, xld, BT > 256u ? BT / 2u : BT)) return fail(c, -12, "gemm: the token tensor map could not be encoded");
   if (p.enc == P0P_ENC_F16) {
     if (!make_map(&mw, reinterpret_cast<const __half*>(p.W) + p.wk0, p.K, p.Nw, p.wG, 128u)) return fail(c, -12, "gemm: the weight tensor map could not be encoded");
   } else mw = mx;

@@ -137,6 +137,64 @@ def test_ref_conv3_ring_bit_identical(gpu, oracle, kernel):
         for x in (s["xb"], s["wb"], ya, yb, ring): gpu.free(x)
 
 
+# ---- conv3 on the tensor-core kernel: clips whose channel count lets a 64-k step stay inside one tap ---------------------
+TC_CLIPS = [
+    dict(name="128-token tiles, fp16 weights", T=5, H=8, W=16, C=64, N=128, enc="f16"),
+    dict(name="384-token tiles (two multiplies per step), fp16 weights, bias", T=4, H=8, W=48, C=64, N=128, enc="f16", bias=True),
+    dict(name="q4 weights (operand in tensor memory), 256 output channels", T=4, H=4, W=32, C=128, N=256, enc="q4"),
+    dict(name="q8 weights, 320-token tiles", T=3, H=4, W=80, C=64, N=128, enc="q8"),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("clip", TC_CLIPS, ids=[c["name"] for c in TC_CLIPS])
+def test_conv3_tensor_core(gpu, oracle, clip):
+    """conv3 through the tcgen05 kernel (the clip read by 4-D tensor-map boxes, zero padding from the out-of-range fill):
+    against the CPU convolution, and whole clip == 2-frame chunks == ring of 3 frames bit for bit"""
+    O = oracle
+    T, H, W, C, N, enc = (clip[k] for k in ("T", "H", "W", "C", "N", "enc"))
+    K = 27 * C
+    X = O.round_f16(O.randn(T * H * W * C, 131)); W0 = O.randn(N * K, 133, 0.03)
+    if enc == "f16": Wref = O.round_f16(W0); wbytes = P().toF16(Wref); encn = "f16"
+    elif enc == "q4": wbytes, Wref = O.pack_q4(W0, N, K); encn = "q4g32a.t64"
+    else: wbytes, Wref = O.pack_q8(W0, N, K); encn = "q8g64s.t64"
+    bias = O.randn(N, 135, 0.1) if clip.get("bias") else None
+    xb, wb = gpu.upload(P().toF16(X)), gpu.upload(wbytes)
+    n = T * H * W * N; fx, fy = H * W * C, H * W * N * 2
+    ya, yb, yc, ring = gpu.buffer(n * 2), gpu.buffer(n * 2), gpu.buffer(n * 2), gpu.buffer(3 * fx * 2)
+    bb = gpu.upload(bias) if bias is not None else None
+    X16 = P().toF16(X)
+
+    def run(x, y, t0, nf, padL=0, ks=1):
+        a = {"w": {"enc": encn, "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": x, "y": y, "M": nf * H * W, "N": N, "K": K,
+             "conv": {"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": t0, "padL": padL, "ks": ks}}
+        if bb is not None: a["epi"] = "bias"; a["ev"] = {"buf": bb}
+        P().gemm(gpu, a)
+        assert P()._lib.KERNEL_NAMES.get(gpu.lastKernel) == "umma", "conv3 did not take the tensor-core kernel"
+
+    try:
+        run({"buf": xb}, {"buf": ya}, 0, T)
+        got = P().fromF16(gpu.read(ya, 0, n * 2).view(np.uint16))
+        want = O.cpu_conv3(X, Wref, T, H, W, C, N)
+        if bias is not None: want = (want.reshape(-1, N) + bias[None, :]).astype(np.float32).ravel()
+        assert O.compare(got, want)[0] > 0.9995
+        CS.check(P().toF16(got), O.to_f16(want), "conv3 tensor core")
+        for t0 in range(0, T, 2):
+            padL = max(0, t0 - 1)
+            run({"buf": xb, "off": padL * fx * 2}, {"buf": yb, "off": t0 * fy}, t0, min(2, T - t0), padL)
+        for t in range(T):
+            for g in sorted({max(0, t - 1), t, min(T - 1, t + 1)}):
+                gpu.device.queue.writeBuffer(ring, (g % 3) * fx * 2, X16, g * fx, fx)
+            run({"buf": ring}, {"buf": yc, "off": t * fy}, t, 1, 0, 3)
+            gpu.done()
+        a, b, c = (gpu.read(y, 0, n * 2).view(np.uint16) for y in (ya, yb, yc))
+        assert np.array_equal(a, b), "chunked conv3 DIFFERS from the whole clip"
+        assert np.array_equal(a, c), "ring conv3 DIFFERS from the whole clip"
+    finally:
+        for x in (xb, wb, ya, yb, yc, ring, bb):
+            if x is not None: gpu.free(x)
+
+
 def test_ref_converted_bf16_linear_q4(gpu, oracle):
     """a BF16 linear layer, converted to 4-bit, through the GEMM (test/kernels.test.js:198-209)"""
     O = oracle
