@@ -395,16 +395,18 @@ inline bool make_map_clip(CUtensorMap* m, const void* base, uint32_t Ci, uint32_
 // or from a ring must take the same tiles (the results are required to be bit-identical).  0 = no tile shape fits.
 inline uint32_t conv3_tile_rows(const KP& p, bool atm) {
   if (p.Wo > 256u || p.Wo % 8u) return 0u;
-  const uint32_t bt_max = 384u;
-  for (uint32_t R = std::min(p.Ho, bt_max / p.Wo); R >= 1u; R--) {
+  // Quantised weights (operand in tensor memory): the fewest rows that give a tile of at least 128 tokens (small tiles
+  // spread better over the SMs, a chunk of a few frames has few tiles, and two accumulators share the k loop).  fp16
+  // weights (both operands through shared memory, whose bandwidth bounds the k-step): the largest tile that fits.
+  uint32_t best = 0u;
+  for (uint32_t R = 1u; R <= p.Ho && R * p.Wo <= 384u; R++) {
     const uint32_t bt = R * p.Wo;
-    if (p.Ho % R) continue;
+    if (p.Ho % R || bt < 16u) continue;
     if (bt <= 256u ? bt % 16u != 0u : (R % 2u != 0u || bt % 32u != 0u)) continue;
-    if (bt < 16u) continue;
-    (void)atm;
-    return R;
+    best = R;
+    if (atm && bt >= 128u) break;
   }
-  return 0u;
+  return best;
 }
 
 inline bool umma_supported(const p0p_ctx*, const KP& p) {
@@ -479,8 +481,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // for the exposed epilogue.
   const uint32_t acc_cols = atm ? 192u : 256u;
   u.KSPLIT = BT * 4u <= acc_cols ? 4u : BT * 2u <= acc_cols ? 2u : 1u;
-  if (atm && u.KSPLIT == 1u && BT <= 192u && KSn >= 32u && p.xmode != P0P_X_CONV3) { u.KSPLIT = 2u; u.NACC = 1u; }
-  if (p.xmode == P0P_X_CONV3) u.KSPLIT = 1u;      // one accumulation order for every call on the same clip
+  if (atm && u.KSPLIT == 1u && BT <= acc_cols && KSn >= 24u) { u.KSPLIT = 2u; u.NACC = 1u; }      // (depends on K and the tile only: conv3 chunks and the whole clip agree)
   u.NS = (BT > 256u || (!atm && BT > 192u)) ? 3u : 4u;
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
