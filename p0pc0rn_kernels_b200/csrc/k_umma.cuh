@@ -49,6 +49,9 @@ struct UmmaP {
   uint32_t n_tiles, m_tiles;
   uint32_t G;           // token tiles per group of the tile order (tile_coords)
   uint32_t cvR;         // conv3: image rows per token tile (tile = cvR x Wo output positions of one frame)
+  uint32_t S, ks_per;   // split-K: units = tiles x S, each over ks_per k-steps; S > 1 leaves fp32 partial sums in sk_part
+  float* sk_part;       // [S][m_tiles * BT][sk_ld] partial sums (k_umma_finish adds them and applies the epilogue)
+  uint32_t sk_ld;
   int* status;
 };
 
@@ -123,7 +126,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gbase + (tmem_slot - base));
 
-  const uint32_t tiles = u.n_tiles * u.m_tiles, KS = p.K / 64u;
+  const uint32_t tiles = u.n_tiles * u.m_tiles, KS = p.K / 64u, units = tiles * u.S;
   const bool swiglu = p.epi == P0P_EPI_SWIGLU;
 
   if (warp == 0) {
@@ -131,9 +134,10 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     if (lane == 0) {
       Ring r(NS);
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const uint32_t tile = unit % tiles, kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
         uint32_t nt, mt; tile_coords(u, tile, nt, mt);
-        for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
+        for (uint32_t ks = kb; ks < ke; ks++, r.next()) {
           if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
           mbar_expect_tx(full + 8u * r.s, BT * 128u + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u));
           if (p.xmode == P0P_X_CONV3) {
@@ -160,15 +164,16 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       Ring q(NQ);
       bool ok = true;
       const uint32_t last = (p.Nw >> 6) - 1u;                  // record tiles past the weight's end do not exist: their columns are never stored
-      for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const uint32_t tile = unit % tiles, kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
         uint32_t nt, mt; tile_coords(u, tile, nt, mt);
         uint32_t trow[2];
         if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
         else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
         const unsigned char* src0 = p.W + ((size_t)trow[0] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
         const unsigned char* src1 = p.W + ((size_t)trow[1] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
-        for (uint32_t ks = 0; ks < KS; ks += UQ<ENC>::KSUP, q.next()) {
-          const uint32_t bytes = min(UQ<ENC>::KSUP, KS - ks) * UQ<ENC>::RB;
+        for (uint32_t ks = kb; ks < ke; ks += UQ<ENC>::KSUP, q.next()) {
+          const uint32_t bytes = min(UQ<ENC>::KSUP, ke - ks) * UQ<ENC>::RB;
           if (!mbar_wait(wq_empty + 8u * q.s, q.ph ^ 1u, u.status, 202, 500u)) { ok = false; break; }
           mbar_expect_tx(wq_full + 8u * q.s, 2u * bytes);
           bulk_g2s(q_st + q.s * UQ<ENC>::STAGE, src0 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
@@ -185,18 +190,19 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     Ring r(NS);
     uint32_t tl = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, tl++) {
+    for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x, tl++) {
+      const uint32_t kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
       const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
       if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8u * buf, par ^ 1u, u.status, 203, 100u))) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * acc_stride;
-      for (uint32_t ks = 0; ks < KS; ks++, r.next()) {
+      for (uint32_t ks = kb; ks < ke; ks++, r.next()) {
         if (!__all_sync(0xffffffffu, mbar_wait(full + 8u * r.s, r.ph, u.status, 204))) { ok = false; break; }
         tc_fence_after();
         const uint64_t bd = umma_desc_sw128(x_st + r.s * BT * 128u);
         const uint32_t at = tmem_base + U_A_COL0_ATM + r.s * 32u;
         const uint64_t ad = umma_desc_sw128(a_st + r.s * U_A_BYTES);
-        const uint32_t first = ks;                                  // 0 on the tile's first k-step: the first multiply overwrites
+        const uint32_t first = ks - kb;                             // 0 on the unit's first k-step: the first multiply overwrites
         if (elect_one()) {
 #pragma unroll
           for (uint32_t kk = 0; kk < 4u; kk++) {                      // per 16 k: 8 tensor-memory columns / +32 bytes
@@ -224,7 +230,8 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     uint32_t tl = 0, pass = 0;
     bool ok = true;
     const bool vec = epilogue_vec_ok(p);
-    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, tl++) {
+    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x, tl++) {
+      const uint32_t tile = unit % tiles, sp = unit / tiles;
       uint32_t nt, mt; tile_coords(u, tile, nt, mt);
       const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
       if (ok && !mbar_wait(acc_full + 8u * buf, par, u.status, 206, 1000u)) ok = false;
@@ -244,7 +251,12 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
           for (int j = 0; j < U_EPI_TB; j++) acc[j] += ok ? __uint_as_float(r[j]) : 0.0f;
         }
         if (ch + 1u < nchunks) tmem_ld16(t0 + (ch + 1u) * U_EPI_TB, r);      // the next pass's accumulators load behind this pass's work
-        epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
+        if (u.S > 1u) {
+          // split-K: this unit's partial sums, fp32, to its own slab; a warp's store covers 128 bytes of a row
+          float* dst = u.sk_part + ((size_t)sp * u.m_tiles * BT + m0 + ch * U_EPI_TB) * u.sk_ld + nt * 128u + c;
+#pragma unroll
+          for (int j = 0; j < U_EPI_TB; j++) dst[(size_t)j * u.sk_ld] = acc[j];
+        } else epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
       }
       tc_fence_before();
       __syncwarp();
@@ -261,9 +273,10 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     Ring ar(NS), qr(NQ);
     uint32_t sub = 0, turn = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      for (uint32_t ks = 0; ks < KS; ks++) {
-        const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == KS - 1u;
+    for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      const uint32_t kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
+      for (uint32_t ks = kb; ks < ke; ks++) {
+        const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == ke - 1u;
         if (turn == grp) {
           // the record stage is awaited at this group's first use of it only (sub 0 or 1: the groups alternate)
           if ((sub < 2u && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
@@ -338,6 +351,25 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, U_TMEM_COLS); }
+}
+
+// ---- split-K second stage: the S partial sums of 16 tokens x 128 columns are added in split order (deterministic) and
+// the fused epilogue runs on the sum.  grid = (column blocks, 16-token groups), 128 threads.
+__global__ void __launch_bounds__(128) k_umma_finish(const KP p, const float* __restrict__ part, uint32_t S, uint32_t mpad, uint32_t ld) {
+  __shared__ __align__(16) float sh[2 * U_EPI_TB * 132];
+  const uint32_t c = threadIdx.x, nB = blockIdx.x * 128u, m0 = blockIdx.y * U_EPI_TB;
+  float acc[U_EPI_TB];
+#pragma unroll
+  for (int j = 0; j < U_EPI_TB; j++) acc[j] = 0.0f;
+  for (uint32_t sp = 0; sp < S; sp++) {
+    const float* src = part + ((size_t)sp * mpad + m0) * ld + nB + c;
+    float v[U_EPI_TB];
+#pragma unroll
+    for (int j = 0; j < U_EPI_TB; j++) v[j] = __ldcg(src + (size_t)j * ld);      // rows up to the slab's padding exist
+#pragma unroll
+    for (int j = 0; j < U_EPI_TB; j++) acc[j] += v[j];
+  }
+  epilogue_cols<U_EPI_TB>(p, m0, nB, c, acc, sh, 1, epilogue_vec_ok(p), 0u);
 }
 
 // ---- fused-norm prologue as one pass: X fp32 [M][ldx] -> X' fp16 [M][K] (src/ops/gemm.js:63-67)
@@ -438,17 +470,10 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   UmmaP u{};
   const uint32_t sms = (uint32_t)c->prop.multiProcessorCount;
   // ---- the fused norm prologue becomes one pass into an fp16 scratch copy of the tokens
-  const void* xbase; uint64_t xld;
-  if (p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD) {
-    const uint64_t bytes = (uint64_t)p.M * p.K * 2u;
-    if (int r = ensure_scratch(c, bytes + 256)) return r;
-    const size_t n4 = (size_t)p.M * p.K / 4u;
-    k_prologue_f16<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(p, reinterpret_cast<__half*>(c->scratch));
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(c, e, "prologue launch");
-    c->launches += 1;
-    xbase = c->scratch; xld = p.K;
-  } else if (p.xmode == P0P_X_CONV3) { xbase = p.X; xld = 0; }
+  const void* xbase = nullptr; uint64_t xld = 0, pro_bytes = 0;
+  const bool pre = p.xmode == P0P_X_RMS || p.xmode == P0P_X_LNMOD;
+  if (pre) { pro_bytes = ((uint64_t)p.M * p.K * 2u + 255u) & ~255ull; xld = p.K; }      // (launched below, once the scratch is sized)
+  else if (p.xmode == P0P_X_CONV3) { xbase = p.X; xld = 0; }
   else { xbase = reinterpret_cast<const __half*>(p.X) + p.kx0; xld = p.ldx; }
   // ---- tile shape.  fp16 weights: both operands in shared memory, up to 256 tokens, two accumulators.  Quantised
   // weights (operand in tensor memory): up to 192 tokens with two accumulators, or up to 384 with one; the cheapest
@@ -489,6 +514,34 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (100 * 1024 + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
   if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
   u.m_tiles = (p.M + BT - 1u) / BT;
+  // ---- split-K: when the tiles leave SMs idle (few output columns) or the last round is nearly empty, each tile's k loop
+  // is cut into S units whose fp32 partial sums a second kernel adds.  Never for conv3 (S would depend on M, and chunked
+  // and whole-clip calls must add in the same order).
+  u.S = 1u; u.ks_per = KSn;
+  if (p.xmode != P0P_X_CONV3) {
+    const uint64_t tiles = (uint64_t)u.n_tiles * u.m_tiles;
+    const uint64_t kstep = std::max<uint64_t>(5u * BT / 2u, 750u), epi = 24u * BT;
+    uint64_t best = ((tiles + sms - 1) / sms) * (KSn * kstep + (u.NACC == 1u ? epi : 0u));
+    for (uint32_t S = 2u; S <= 16u; S++) {
+      const uint32_t per = (KSn + S - 1u) / S;
+      if (per < 8u || (uint64_t)(S - 1u) * per >= KSn) continue;                     // every unit gets k-steps, at least 8 each
+      const uint64_t cost = ((tiles * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u + (uint64_t)S * BT * 40u;   // + pipeline fill per unit; second kernel: launch, partials written and read
+      if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; }
+    }
+  }
+  const uint64_t sk_bytes = u.S > 1u ? (uint64_t)u.S * u.m_tiles * BT * u.n_tiles * 128u * 4u : 0u;
+  if (pro_bytes + sk_bytes) {
+    if (int r = ensure_scratch(c, pro_bytes + sk_bytes + 256)) return r;
+  }
+  if (pre) {
+    const size_t n4 = (size_t)p.M * p.K / 4u;
+    k_prologue_f16<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(p, reinterpret_cast<__half*>(c->scratch));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(c, e, "prologue launch");
+    c->launches += 1;
+    xbase = c->scratch;
+  }
+  u.sk_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(c->scratch) + pro_bytes); u.sk_ld = u.n_tiles * 128u;
   {   // a wave of `sms` tiles reads G token tiles and sms / G weight tiles: least bytes at G = sqrt(sms * weight tile / token tile)
     const double wt = 128.0 * (p.enc == P0P_ENC_Q4 ? 0.625 : p.enc == P0P_ENC_Q8 ? 1.03125 : 2.0), xt = 2.0 * BT;
     const double g = std::sqrt((double)sms * wt / xt);
@@ -506,7 +559,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
   const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 512u);
-  const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles, sms);
+  const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles * u.S, sms);
   const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
   static bool ready = false;
@@ -525,6 +578,11 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   else k_gemm_umma<P0P_ENC_F16, false><<<grid, U_THREADS, smem, c->stream>>>(u, mx, mw);
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");
   c->launches += 1;
+  if (u.S > 1u) {
+    k_umma_finish<<<dim3(u.n_tiles, (p.M + U_EPI_TB - 1u) / U_EPI_TB), 128, 0, c->stream>>>(p, u.sk_part, u.S, u.m_tiles * BT, u.sk_ld);
+    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "split-K second stage launch");
+    c->launches += 1;
+  }
   return 0;
 }
 

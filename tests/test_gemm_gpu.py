@@ -304,6 +304,11 @@ UMMA = [
     dict(name="u q8 M520 3 token tiles", enc="q8", M=520, N=256, K=1024),
     dict(name="u f16 M200 ld", enc="f16", M=200, N=320, K=448, w_ld=456, w_cols=456, wr0=5, w_rows=330),
     dict(name="u q4 M17", enc="q4", M=17, N=256, K=256),
+    dict(name="u split-K q4 M64 K4096", enc="q4", M=64, N=256, K=4096),
+    dict(name="u split-K q8 M300 resadd", enc="q8", M=300, N=128, K=2048, epi="resadd"),
+    dict(name="u split-K lnmod+heads", enc="q8", M=100, N=384, K=1536, xmode="lnmod", epi="heads", heads=dict(Ltot=128, Hq=1, Hkv=1, rowOff=7, eps=1e-6)),
+    dict(name="u split-K rms+swiglu bias", enc="q4", M=40, N=512, K=2048, xmode="rms", epi="swiglu", bias=True),
+    dict(name="u split-K f16 weights ragged K split", enc="f16", M=90, N=256, K=1600),
     dict(name="u q4 M384 one wide tile, ring wrap", enc="q4", M=384, N=640, K=1280),
     dict(name="u q8 M777 wide tiles, many", enc="q8", M=777, N=2560, K=448, epi="resadd"),
     dict(name="u q4 M250 single accumulator, narrow", enc="q4", M=250, N=1280, K=192, epi="swiglu"),
