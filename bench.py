@@ -450,11 +450,13 @@ def main():
     hp = C.c_void_p(); gpu._check(lib.p0p_host_alloc(gpu._h, M * HID * 4, C.byref(hp)))
     pin_in = np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_float)), shape=(M * HID,)); pin_in[:] = x_host[: M * HID]
     out_bytes = M * HID * 4
+    hq = C.c_void_p(); gpu._check(lib.p0p_host_alloc(gpu._h, out_bytes, C.byref(hq)))
+    pin_out = np.ctypeslib.as_array(C.cast(hq, C.POINTER(C.c_uint8)), shape=(out_bytes,))       # page-locked destination of the step's result
 
     def e2e_step(i):
         gpu.upload(pin_in, "", xb, 0)           # the step's tokens (fp32 residual stream), page-locked host -> device
         block(M, i)
-        return gpu.read(xb, 0, out_bytes)       # the updated residual stream, device -> host
+        return gpu.read(xb, 0, out_bytes, out=pin_out)       # the updated residual stream, device -> page-locked host
 
     for s in range(3): e2e_step(s % args.copies)
     torch.cuda.synchronize()

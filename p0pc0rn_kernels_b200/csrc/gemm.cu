@@ -142,11 +142,14 @@ extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a, double* flops) {
   // from a ring must give the bits of the whole-clip call (test/kernels.test.js:123-145).
   int want = (int)a->force_kernel, used = 0;
   int rc = 0;
-  if (want == P0P_K_DECODE || (want == P0P_K_AUTO && decode_supported(p))) {
-    if (!decode_supported(p)) return fail(c, -9, "gemm: the decode kernel does not take this configuration");
+  // The streaming kernel wins up to 8 tokens (it never dequantises); from 9 on its second token group doubles its work and
+  // the tensor-core kernel (narrow tiles, K-split accumulators, split-K) is faster on every shape measured.
+  const bool dec_ok = decode_supported(p), um_ok = umma_supported(c, p);
+  if (want == P0P_K_DECODE || (want == P0P_K_AUTO && dec_ok && (p.M <= 8u || !um_ok))) {
+    if (!dec_ok) return fail(c, -9, "gemm: the decode kernel does not take this configuration");
     rc = launch_decode(c, p); used = P0P_K_DECODE;
-  } else if (want == P0P_K_UMMA || (want == P0P_K_AUTO && umma_supported(c, p))) {
-    if (!umma_supported(c, p)) return fail(c, -9, "gemm: the tensor-core kernel does not take this configuration");
+  } else if (want == P0P_K_UMMA || (want == P0P_K_AUTO && um_ok)) {
+    if (!um_ok) return fail(c, -9, "gemm: the tensor-core kernel does not take this configuration");
     rc = launch_umma(c, p); used = P0P_K_UMMA;
   } else {
     cudaError_t e = launch_generic(p, c->stream);

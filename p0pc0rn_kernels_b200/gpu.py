@@ -177,10 +177,12 @@ class Gpu:
         self._write(b, dstOff, raw)
         return b
 
-    def read(self, buf: Buffer, off=0, size=None) -> np.ndarray:
-        """[off, off+size) of a buffer as a uint8 array; waits for queued work (src/core/gpu.js:150-170)."""
+    def read(self, buf: Buffer, off=0, size=None, out=None) -> np.ndarray:
+        """[off, off+size) of a buffer as a uint8 array; waits for queued work (src/core/gpu.js:150-170).  `out` (not in the
+        reference): a caller's array of at least `size` bytes to read into, e.g. page-locked memory from p0p_host_alloc."""
         size = buf._pf - off if size is None else size
-        out = np.empty(int(size), np.uint8)
+        if out is None: out = np.empty(int(size), np.uint8)
+        elif out.nbytes < size or not out.flags["C_CONTIGUOUS"]: raise ValueError("read: `out` must be a contiguous array of at least `size` bytes")
         if size:
             self._check(lib.p0p_read(self._h, buf.handle, int(off), out.ctypes.data_as(C.c_void_p), int(size)))
         return out
