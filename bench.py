@@ -343,10 +343,32 @@ def main():
         return gpu.wrap(t.data_ptr(), t.numel() * t.element_size())
 
     st_t = torch.zeros(Mmax * 2, dtype=torch.float32, device=dev); st = wrap(st_t)
-    x_t = torch.zeros(Mmax * HID, dtype=torch.float32, device=dev); xb = wrap(x_t)                  # residual stream in (fp32)
-    hl_t = torch.zeros(Mmax * ffl, dtype=torch.float16, device=dev); hl = wrap(hl_t)                # this rank's SwiGLU columns
-    hf_t = hl_t if world == 1 else torch.zeros(Mmax * FF, dtype=torch.float16, device=dev)          # the full hidden row
-    hf = hl if world == 1 else wrap(hf_t)
+    class DevView:
+        """a library buffer as a torch tensor (no copy), through the CUDA array interface"""
+        def __init__(self, buf, n, typestr):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (buf.ptr, False), "version": 2}
+
+    # the residual stream and the full hidden row live in library buffers (cudaMalloc), so that other ranks can map them
+    xb = gpu.buffer(Mmax * HID * 4, "residual", shareable=world > 1); x_t = torch.as_tensor(DevView(xb, Mmax * HID, "<f4"), device=dev)      # residual stream (fp32)
+    hl_t = torch.zeros(Mmax * ffl, dtype=torch.float16, device=dev); hl = wrap(hl_t)                # this rank's SwiGLU columns (gather path)
+    if world == 1: hf, hf_t = hl, hl_t
+    else: hf = gpu.buffer(Mmax * FF * 2, "hidden", shareable=True); hf_t = torch.as_tensor(DevView(hf, Mmax * FF, "<f2"), device=dev)   # the full hidden row
+    # ---- N > 1: every rank maps the others' hidden and residual buffers; the epilogues then store each rank's columns into all
+    # copies (peer stores over NVLink) and a one-element all-reduce orders the ranks, instead of an all-gather plus re-layout
+    hf_peers, x_peers, fused = [], [], False
+    if world > 1 and os.environ.get("P0P_BENCH_GATHER", "") != "nccl":
+        try:
+            mine = (gpu.ipcExport(hf), gpu.ipcExport(xb)); every = [None] * world
+            dist.all_gather_object(every, mine)
+            for r, (hh, hx) in enumerate(every):
+                if r != rank:
+                    hf_peers.append(gpu.ipcOpen(hh, Mmax * FF * 2, f"hidden@{r}")); x_peers.append(gpu.ipcOpen(hx, Mmax * HID * 4, f"residual@{r}"))
+            fused = True
+        except Exception as e:                                                   # no peer access on this box: the NCCL gather path below
+            if rank == 0: print(f"peer mapping failed ({e}); using NCCL all-gathers", file=sys.stderr)
+            hf_peers, x_peers, fused = [], [], False
+        ok_t = torch.tensor([1 if fused else 0], device=dev); dist.all_reduce(ok_t, op=dist.ReduceOp.MIN); fused = bool(ok_t.item())
+    flag_t = torch.zeros(1, dtype=torch.float32, device=dev)
     x_host = np.random.default_rng(5).standard_normal(Mmax * HID).astype(np.float32)
     x_t.copy_(torch.from_numpy(x_host))
     launches = {"n": 0}
@@ -354,18 +376,21 @@ def main():
     def block(M, i, gather=True):
         """one pass of the MLP block over M tokens with weight copy i"""
         P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
+        yh = {"buf": hf, "ld": FF, "n0": rank * ffl, "peers": hf_peers} if fused else {"buf": hl, "ld": ffl}
         a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
-             "y": {"buf": hl, "ld": ffl}, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
+             "y": yh, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
         if args.kernel: a["kernel"] = args.kernel
         P.gemm(gpu, a)
-        if world > 1 and gather:
+        if fused and gather: dist.all_reduce(flag_t)                                # every rank's columns are in every copy once all ranks are here
+        elif world > 1 and gather:
             hf_t[: M * FF].view(M, FF).copy_(P.all_gather_columns(hl_t[: M * ffl].view(M, ffl)))
         # residual add, in place, into this rank's columns of the (replicated) fp32 residual stream
         a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
-             "y": {"buf": xb, "ld": HID, "n0": rank * hidl}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
+             "y": {"buf": xb, "ld": HID, "n0": rank * hidl, "peers": x_peers if fused else []}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
         if args.kernel: a["kernel"] = args.kernel
         P.gemm(gpu, a)
-        if world > 1 and gather:
+        if fused and gather: dist.all_reduce(flag_t)
+        elif world > 1 and gather:
             xv = x_t[: M * HID].view(M, HID)
             xv.copy_(P.all_gather_columns(xv[:, rank * hidl:(rank + 1) * hidl]))
 
@@ -500,18 +525,20 @@ def main():
 
     if rank == 0:
         # CPU baseline: the oracle port on a bounded sample, all host threads
-        import oracle as O
-        O.build(); thr = O.max_threads()
-        cpu_sample(1, 256, 128, thr)
-        cm = min(M, 512)
-        f, d = cpu_sample(cm, FF // 2, HID // 2, thr, reps=4)
-        cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port",
-               "sample": f"{cm} tokens x {FF // 2} of {FF} hidden columns (gate/up) + {HID // 2} of {HID} output columns (down), 4 passes, float64 accumulate, {d:.1f} s"}
+        cpu = None
+        if world == 1:                       # the CPU baseline is a single-GPU-run figure (and torchrun pins its ranks to one thread)
+            import oracle as O
+            O.build(); thr = O.max_threads()
+            cpu_sample(1, 256, 128, thr)
+            cm = min(M, 512)
+            f, d = cpu_sample(cm, FF // 2, HID // 2, thr, reps=4)
+            cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port",
+                   "sample": f"{cm} tokens x {FF // 2} of {FF} hidden columns (gate/up) + {HID // 2} of {HID} output columns (down), 4 passes, float64 accumulate, {d:.1f} s"}
         out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (q4 weights dequantised in-kernel)",
                "data": "synthetic",
                "config": {"workload": f"LLM MLP block q4, M={M} tokens: rowstats + gate/up K4096->2x14336 (rms, swiglu) + down K14336->4096 (resadd) (configs[1])",
-                          "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + (" + NCCL all-gather of hidden and output" if world > 1 else ""),
+                          "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + ("" if world == 1 else " + epilogues store each rank's columns into every rank's buffers (peer stores), one-element all-reduce as barrier" if fused else " + NCCL all-gather of hidden and output"),
                           "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)"},
                "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
                "GB/s": block_bytes(M) / (ms * 1e-3) / 1e9}

@@ -133,6 +133,13 @@ typedef struct p0p_gemm_args {
   uint64_t x_off, w_off, y_off;    /* bytes */
   uint64_t w_bytes;                /* w.bytes (size of the encoded tensor) */
   uint64_t x_size, y_size;         /* x.size / y.size when given, else 0 = to the end of the buffer */
+  /* No counterpart in the reference (multi-GPU extension): peer copies of y.  Every result is stored to y AND, at the same
+   * byte offset, to each y_peers[i] - device memory of another GPU opened with p0p_ipc_open.  This is the all-gather of an
+   * N-sharded output fused into the store: each rank writes its columns into every rank's full-row buffer (y.ld = full N,
+   * y.n0 = the rank's first column); the caller still orders the ranks (any stream-ordered barrier) before the rows are read.
+   * Plain peer stores over NVLink; nothing waits inside the kernel. */
+  uint32_t n_ypeers, reserved0;
+  p0p_buf* y_peers[7];
 } p0p_gemm_args;
 
 /* gemm(gpu, a) (src/ops/gemm.js:268-327): validates, picks the kernel, enqueues.  *flops = 2*M*N*K. */
@@ -156,6 +163,15 @@ uint64_t p0p_launch_count(const p0p_ctx* ctx);
 #define P0P_STATIC_SCRATCH_BYTES (8u << 20)
 int p0p_decode_q4_static(int device, void* stream, const void* w, const void* x, void* y, uint32_t M, uint32_t N, uint32_t K,
                          char* err, size_t err_cap);
+
+/* Peer memory (no counterpart in the reference).  p0p_alloc_shareable is p0p_alloc (zeroed, 16-byte rounded, counted) on
+ * memory that other processes can map: plain cudaMalloc instead of the stream-ordered pool, never recycled.
+ * p0p_ipc_export writes the 64-byte CUDA IPC handle of such a buffer (whole allocation) to `handle64`; p0p_ipc_open maps the allocation another process exported (on another GPU of
+ * the node) and returns it as a non-owning buffer of `bytes` bytes, unmapped by p0p_free.  Such a buffer is valid as a
+ * y_peers entry of p0p_gemm; pass the handle bytes between processes by any means. */
+int p0p_alloc_shareable(p0p_ctx* ctx, uint64_t bytes, p0p_buf** out);
+int p0p_ipc_export(p0p_ctx* ctx, const p0p_buf* buf, void* handle64);
+int p0p_ipc_open(p0p_ctx* ctx, const void* handle64, uint64_t bytes, p0p_buf** out);
 
 /* Debug op: writes the fp16 tile values the kernels feed to the multiply, rows [r0, r0+nr) x all w_cols
  * columns, row-major into `out` (fp16).  path 0 = the fp32-FMA conversion, 1 = the packed half2 conversion

@@ -15,7 +15,7 @@ SYMBOLS = [
     "p0p_alloc", "p0p_wrap", "p0p_free", "p0p_drain_pool", "p0p_pool_stats", "p0p_reset_peak", "p0p_buf_size", "p0p_buf_ptr",
     "p0p_write", "p0p_read", "p0p_clear", "p0p_copy", "p0p_sync", "p0p_host_alloc", "p0p_host_free",
     "p0p_capture_begin", "p0p_capture_end", "p0p_graph_launch", "p0p_graph_free",
-    "p0p_decode_q4_static",
+    "p0p_decode_q4_static", "p0p_alloc_shareable", "p0p_ipc_export", "p0p_ipc_open",
     "p0p_gemm", "p0p_last_kernel", "p0p_launch_count", "p0p_dequant", "p0p_rowstats",
     "p0p_f2h", "p0p_h2f", "p0p_to_f16", "p0p_from_f16", "p0p_pack_q4", "p0p_pack_q8", "p0p_reorder_conv_rows",
     "p0p_encoded_bytes", "p0p_shard_rows", "p0p_abi_version",
@@ -40,7 +40,8 @@ class GemmArgs(C.Structure):
                 + [(n, C.c_uint32) for n in ("pv_off", "pv_stride", "ev_off", "st_off", "bv_off", "bv_up", "Hi", "Wi", "Ci", "Ho", "Wo",
                                               "stride", "padT", "padL", "ks", "tile_bm", "tile_bn", "acc_f16", "force_kernel")]
                 + [(n, C.c_void_p) for n in ("x", "w", "y", "st", "pv", "ev", "bv", "rp", "gt")]
-                + [(n, C.c_uint64) for n in ("x_off", "w_off", "y_off", "w_bytes", "x_size", "y_size")])
+                + [(n, C.c_uint64) for n in ("x_off", "w_off", "y_off", "w_bytes", "x_size", "y_size")]
+                + [("n_ypeers", C.c_uint32), ("reserved0", C.c_uint32), ("y_peers", C.c_void_p * 7)])
 
 
 def _load():
@@ -58,6 +59,7 @@ def _load():
         "p0p_copy": (i, [vp, vp, u64, vp, u64, u64]), "p0p_sync": (i, [vp]), "p0p_host_alloc": (i, [vp, u64, C.POINTER(vp)]), "p0p_host_free": (i, [vp, vp]),
         "p0p_capture_begin": (i, [vp]), "p0p_capture_end": (i, [vp, C.POINTER(vp)]), "p0p_graph_launch": (i, [vp, vp]), "p0p_graph_free": (i, [vp, vp]),
         "p0p_decode_q4_static": (i, [i, vp, vp, vp, vp, u32, u32, u32, C.c_char_p, C.c_size_t]),
+        "p0p_alloc_shareable": (i, [vp, u64, C.POINTER(vp)]), "p0p_ipc_export": (i, [vp, vp, vp]), "p0p_ipc_open": (i, [vp, vp, u64, C.POINTER(vp)]),
         "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]),
         "p0p_dequant": (i, [vp, u32, vp, u64, u32, u32, u32, u32, u32, vp, u64]),
         "p0p_rowstats": (i, [vp, vp, u64, u32, u32, u32, u32, u32, C.c_float, vp, u32]),

@@ -23,6 +23,8 @@ struct KP {
   const uint8_t* W;  // encoded weights, at w.off
   void* Y;           // fp16 or fp32, at y.off
   const float* ST; const float* PV; const float* EV; const float* BV; const float* RP; const __half* GT;
+  uint32_t nyp;      // peer copies of Y: every store to Y is repeated at the same offset of YP[0..nyp)
+  void* YP[7];
 };
 
 // ---- activations ------------------------------------------------------------------------------------

@@ -15,6 +15,8 @@ struct p0p_buf {
   void* ptr = nullptr;
   uint64_t size = 0;      // the reference's _pf
   bool owned = true;      // false: wrapped foreign memory
+  bool ipc = false;       // a peer allocation mapped by p0p_ipc_open (unmapped on free)
+  bool plain = false;     // cudaMalloc'd outside the stream-ordered pool (p0p_alloc_shareable): has an IPC handle, never pooled
   uint64_t seq = 0;       // pool age
 };
 

@@ -9,6 +9,25 @@ namespace p0p {
 
 __device__ __forceinline__ void bar_sync_named(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
 
+// ---- stores.  Every result goes to Y and, at the same offset, to the peer copies of Y (other GPUs' buffers: the
+// all-gather of an N-sharded output fused into the store; nyp is 0 on one GPU and the loops vanish).
+__device__ __forceinline__ void put_h(const KP& p, size_t i, __half v) {
+  reinterpret_cast<__half*>(p.Y)[i] = v;
+  for (uint32_t q = 0; q < p.nyp; q++) reinterpret_cast<__half*>(p.YP[q])[i] = v;
+}
+__device__ __forceinline__ void put_f(const KP& p, size_t i, float v) {
+  reinterpret_cast<float*>(p.Y)[i] = v;
+  for (uint32_t q = 0; q < p.nyp; q++) reinterpret_cast<float*>(p.YP[q])[i] = v;
+}
+__device__ __forceinline__ void put_h8(const KP& p, size_t i, uint4 v) {        // 8 halves, i a multiple of 8
+  *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.Y) + i) = v;
+  for (uint32_t q = 0; q < p.nyp; q++) *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.YP[q]) + i) = v;
+}
+__device__ __forceinline__ void put_f4(const KP& p, size_t i, float4 v) {       // 4 floats, i a multiple of 4
+  *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.Y) + i) = v;
+  for (uint32_t q = 0; q < p.nyp; q++) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.YP[q]) + i) = v;
+}
+
 // ---- row-wise stores.  A thread owns a column, so its own stores are 2 or 4 bytes wide and a warp's store covers 64
 // or 128 bytes of a row.  With `vec` the TB x 128 results of a pass go through shared memory instead and leave as
 // 16-byte stores along the rows: an eighth of the store instructions.  The staging area is double-buffered by the
@@ -26,15 +45,15 @@ __device__ __forceinline__ bool epilogue_vec_ok(const KP& p) {
     default: return false;
   }
 }
-// fp16 results st[TB][W] (W = 128, or 64 for the gate|up epilogue) -> rows of Y.  ybase: element (row m0, first column of the
-// block); valid: columns of the block that exist (a multiple of 8).
+// fp16 results st[TB][W] (W = 128, or 64 for the gate|up epilogue) -> rows of Y.  ybase: element index of (row m0, first
+// column of the block); valid: columns of the block that exist (a multiple of 8).
 template <int TB, int W>
-__device__ __forceinline__ void rows_out_f16(const KP& p, const __half* st, uint32_t t, uint32_t m0, __half* ybase, size_t row_stride, uint32_t valid) {
+__device__ __forceinline__ void rows_out_f16(const KP& p, const __half* st, uint32_t t, uint32_t m0, size_t ybase, size_t row_stride, uint32_t valid) {
   constexpr int CPR = W / 8;                      // 16-byte pieces per row
 #pragma unroll
   for (int i = 0; i < TB * CPR / 128; i++) {
     const uint32_t idx = (uint32_t)i * 128u + t, row = idx / CPR, ch = idx % CPR;
-    if (m0 + row < p.M && ch * 8u < valid) *reinterpret_cast<uint4*>(ybase + (size_t)row * row_stride + ch * 8u) = *reinterpret_cast<const uint4*>(st + row * W + ch * 8u);
+    if (m0 + row < p.M && ch * 8u < valid) put_h8(p, ybase + (size_t)row * row_stride + ch * 8u, *reinterpret_cast<const uint4*>(st + row * W + ch * 8u));
   }
 }
 
@@ -42,7 +61,6 @@ __device__ __forceinline__ void rows_out_f16(const KP& p, const __half* st, uint
 template <int TB, bool GELU>
 __device__ __forceinline__ void swiglu_tokens(const KP& p, uint32_t m0, uint32_t col, uint32_t c, const float (&acc)[TB], float gB, float uB, float* sh, bool vec, uint32_t par) {
   const uint32_t o = col >> 1, odd = c & 1u;
-  __half* Yh = reinterpret_cast<__half*>(p.Y);
   // branch-free arithmetic first (a branch per token would end the scheduler's view at every token and serialise
   // the eight exp / reciprocal chains), then the stores
   __half out[TB / 2];
@@ -60,7 +78,7 @@ __device__ __forceinline__ void swiglu_tokens(const KP& p, uint32_t m0, uint32_t
   } else if (col < p.N) {
 #pragma unroll
     for (int j = 0; j < TB; j += 2)
-      if (m0 + j + odd < p.M) Yh[(size_t)(m0 + j + odd) * p.ldy + p.ny0 + o] = out[j / 2];
+      if (m0 + j + odd < p.M) put_h(p, (size_t)(m0 + j + odd) * p.ldy + p.ny0 + o, out[j / 2]);
   }
 }
 
@@ -134,7 +152,7 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
         const uint32_t m = m0 + j;
         if (m < p.M) {
           const float g = __half2float(p.GT[(size_t)m * p.Ltot + p.ny0 + col]);
-          Yh[(size_t)m * p.ldy + p.ny0 + col] = __float2half_rn(v[j] / (1.0f + expf(-g)));
+          put_h(p, (size_t)m * p.ldy + p.ny0 + col, __float2half_rn(v[j] / (1.0f + expf(-g))));
         }
       }
       bar_sync_named(barid, 128);     // `part` is free again
@@ -172,10 +190,10 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     } else {
 #pragma unroll
       for (int j = 0; j < TB; j++)
-        if (m0 + j < p.M) Yh[((size_t)hd * p.Ltot + p.rowOff + m0 + j) * 128u + c] = __float2half_rn(v[j]);
+        if (m0 + j < p.M) put_h(p, ((size_t)hd * p.Ltot + p.rowOff + m0 + j) * 128u + c, __float2half_rn(v[j]));
     }
     bar_sync_named(barid, 128);       // results staged / scratch is free again
-    if (vec) rows_out_f16<TB, 128>(p, reinterpret_cast<const __half*>(sh + TB * 132) + par * TB * 128, c, m0, Yh + ((size_t)hd * p.Ltot + p.rowOff + m0) * 128u, 128u, 128u);
+    if (vec) rows_out_f16<TB, 128>(p, reinterpret_cast<const __half*>(sh + TB * 132) + par * TB * 128, c, m0, ((size_t)hd * p.Ltot + p.rowOff + m0) * 128u, 128u, 128u);
     return;
   }
   if (epi == P0P_EPI_SWIGLU) {
@@ -189,7 +207,7 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     else swiglu_tokens<TB, false>(p, m0, col, c, acc, gB, uB, sh, vec, par);
     if (vec) {
       bar_sync_named(barid, 128);
-      rows_out_f16<TB, 64>(p, reinterpret_cast<const __half*>(sh) + par * TB * 64, c, m0, Yh + (size_t)m0 * p.ldy + p.ny0 + (nB >> 1), p.ldy, nB < p.N ? min(64u, (p.N - nB) >> 1) : 0u);
+      rows_out_f16<TB, 64>(p, reinterpret_cast<const __half*>(sh) + par * TB * 64, c, m0, (size_t)m0 * p.ldy + p.ny0 + (nB >> 1), p.ldy, nB < p.N ? min(64u, (p.N - nB) >> 1) : 0u);
     }
     return;
   }
@@ -201,7 +219,7 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
 #pragma unroll
       for (int j = 0; j < TB; j++) st[j * 128 + c] = __float2half_rn(acc[j] + bias);
       bar_sync_named(barid, 128);
-      rows_out_f16<TB, 128>(p, st, c, m0, Yh + (size_t)m0 * p.ldy + p.ny0 + nB, p.ldy, valid);
+      rows_out_f16<TB, 128>(p, st, c, m0, (size_t)m0 * p.ldy + p.ny0 + nB, p.ldy, valid);
     } else {                                                        // f32 / resadd: fp32 rows, four columns per piece
       float* st = sh + par * TB * 132;
 #pragma unroll
@@ -231,7 +249,7 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
         float4 o;
         if (epi == P0P_EPI_F32) o = a;
         else { o.x = old[i].x + g4[0] * (a.x + b4[0]); o.y = old[i].y + g4[1] * (a.y + b4[1]); o.z = old[i].z + g4[2] * (a.z + b4[2]); o.w = old[i].w + g4[3] * (a.w + b4[3]); }
-        *reinterpret_cast<float4*>(Yf + (size_t)(m0 + row) * p.ldy + p.ny0 + c4) = o;
+        put_f4(p, (size_t)(m0 + row) * p.ldy + p.ny0 + c4, o);
       }
     }
     return;
@@ -257,10 +275,10 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     if (m >= p.M) continue;
     const size_t yi = (size_t)m * p.ldy + p.ny0 + col;
     const float a = acc[j];
-    if (epi == P0P_EPI_F16) Yh[yi] = __float2half_rn(a);
-    else if (epi == P0P_EPI_F32) Yf[yi] = a;
-    else if (epi == P0P_EPI_RESADD) Yf[yi] = old[j] + gate * (a + bias);
-    else Yh[yi] = __float2half_rn(a + bias + old[j]);
+    if (epi == P0P_EPI_F16) put_h(p, yi, __float2half_rn(a));
+    else if (epi == P0P_EPI_F32) put_f(p, yi, a);
+    else if (epi == P0P_EPI_RESADD) put_f(p, yi, old[j] + gate * (a + bias));
+    else put_h(p, yi, __float2half_rn(a + bias + old[j]));
   }
 }
 

@@ -2,6 +2,8 @@
 // bindings gave it for free), kernel choice, launch.  Replaces gemm(gpu, a) of src/ops/gemm.js:268-327.
 // There is no dispatch splitting: the reference cuts work into <= 0.2 s dispatches for the browser GPU
 // watchdog (src/ops/gemm.js:286-292), which a CUDA stream does not need.
+#include <cstring>
+#include <cstddef>
 #include "ctx.h"
 #include "k_generic.cuh"
 #include "k_aux.cuh"
@@ -21,9 +23,15 @@ inline bool live(const p0p_ctx* c, const p0p_buf* b) { return b && c->bufs.count
 extern "C" int p0p_last_kernel(const p0p_ctx* c) { return c ? c->last_kernel : 0; }
 extern "C" uint64_t p0p_launch_count(const p0p_ctx* c) { return c ? c->launches : 0; }
 
-extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a, double* flops) {
+extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a_in, double* flops) {
   P0P_ALIVE(c);
-  if (!a || a->struct_size < sizeof(p0p_gemm_args)) return fail(c, -1, "gemm: bad argument block");
+  // callers built against the argument block without the peer fields pass a shorter struct_size: the rest reads as zero
+  if (!a_in || a_in->struct_size < offsetof(p0p_gemm_args, n_ypeers)) return fail(c, -1, "gemm: bad argument block");
+  p0p_gemm_args a_full;
+  memset(&a_full, 0, sizeof a_full);
+  memcpy(&a_full, a_in, std::min<size_t>(a_in->struct_size, sizeof a_full));
+  const p0p_gemm_args* a = &a_full;
+  if (a->n_ypeers > 7u) return fail(c, -1, "gemm: at most 7 peer copies of y");
   if (a->enc > P0P_ENC_F16) return fail(c, -2, "gemm: unsupported weight encoding %u", a->enc);          // src/ops/gemm.js:271
   if (a->xmode > P0P_X_CONV3 || a->epi > P0P_EPI_ONORMGATE) return fail(c, -2, "gemm: unknown prologue or epilogue");
   const uint32_t M = a->M, N = a->N, K = a->K;
@@ -133,6 +141,13 @@ extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a, double* flops) {
   p.ST = a->st ? (const float*)a->st->ptr : nullptr; p.PV = a->pv ? (const float*)a->pv->ptr : nullptr;
   p.EV = a->ev ? (const float*)a->ev->ptr : nullptr; p.BV = a->bv ? (const float*)a->bv->ptr : nullptr;
   p.RP = a->rp ? (const float*)a->rp->ptr : nullptr; p.GT = a->gt ? (const __half*)a->gt->ptr : nullptr;
+  p.nyp = a->n_ypeers;
+  for (uint32_t q = 0; q < a->n_ypeers; q++) {
+    const p0p_buf* yb = a->y_peers[q];
+    if (!live(c, yb)) return fail(c, -4, "gemm: missing binding y_peers[%u]", q);
+    if (yb->size < a->y->size) return fail(c, -7, "gemm: y_peers[%u] is smaller than y", q);
+    p.YP[q] = (char*)yb->ptr + a->y_off;
+  }
   p.vecx = (a->xmode == P0P_X_F16 && p.ldx % 8u == 0 && p.kx0 % 8u == 0 && ((uintptr_t)p.X & 15u) == 0) ? 1u : 0u;
   p.vecw = (a->enc == P0P_ENC_F16 && p.wG % 8u == 0 && a->wk0 % 8u == 0 && ((uintptr_t)p.W & 15u) == 0) ? 1u : 0u;
   if (a->epi == P0P_EPI_HEADS && ((uintptr_t)p.Y & 15u)) return fail(c, -5, "gemm: heads output must be 16-byte aligned");
@@ -152,6 +167,7 @@ extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a, double* flops) {
     if (!um_ok) return fail(c, -9, "gemm: the tensor-core kernel does not take this configuration");
     rc = launch_umma(c, p); used = P0P_K_UMMA;
   } else {
+    if (p.nyp) return fail(c, -9, "gemm: peer copies of y need the decode or the tensor-core kernel, which do not take this configuration");
     cudaError_t e = launch_generic(p, c->stream);
     if (e != cudaSuccess) return cuda_fail(c, e, "gemm launch");
     c->launches += 1; used = P0P_K_GENERIC;

@@ -46,7 +46,7 @@ static int check_kernel_status(p0p_ctx* c) {
 }
 
 static void destroy_buf(p0p_ctx* c, p0p_buf* b) {
-  if (b->owned && b->ptr) cudaFreeAsync(b->ptr, c->stream);
+  if (b->owned && b->ptr) { if (b->plain) { cudaStreamSynchronize(c->stream); cudaFree(b->ptr); } else cudaFreeAsync(b->ptr, c->stream); }
   delete b;
 }
 
@@ -139,14 +139,56 @@ int p0p_wrap(p0p_ctx* c, void* device_ptr, uint64_t bytes, p0p_buf** out) {
   return 0;
 }
 
+int p0p_alloc_shareable(p0p_ctx* c, uint64_t bytes, p0p_buf** out) {
+  P0P_ALIVE(c);
+  if (!out) return fail(c, -1, "buffer: null result pointer");
+  *out = nullptr;
+  const uint64_t size = bytes < 16 ? 16 : (bytes + 15) / 16 * 16;
+  if (size > c->prop.totalGlobalMem) return fail(c, -2, "buffer %llu B exceeds maxBufferSize", (unsigned long long)size);
+  DeviceGuard g(c->device);
+  p0p_buf* b = new p0p_buf();
+  cudaError_t e = cudaMalloc(&b->ptr, size);             // not the stream-ordered pool: its memory has no IPC handle
+  if (e != cudaSuccess) { delete b; return cuda_fail(c, e, "shareable buffer"); }
+  b->size = size; b->plain = true; c->creates++;
+  e = cudaMemsetAsync(b->ptr, 0, size, c->stream);
+  if (e != cudaSuccess) { cudaFree(b->ptr); delete b; return cuda_fail(c, e, "buffer clear"); }
+  c->bufs.insert(b); c->alive += size;
+  if (c->alive > c->peak) c->peak = c->alive;
+  if (c->alive > c->hw) c->hw = c->alive;
+  *out = b;
+  return 0;
+}
+int p0p_ipc_export(p0p_ctx* c, const p0p_buf* b, void* handle64) {
+  P0P_ALIVE(c);
+  if (!b || !handle64 || !c->bufs.count(const_cast<p0p_buf*>(b)) || !b->owned || !b->plain) return fail(c, -1, "ipc_export: needs a buffer made by p0p_alloc_shareable");
+  DeviceGuard g(c->device);
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+  P0P_CUDA(c, cudaIpcGetMemHandle(&h, b->ptr), "ipc_export");
+  memcpy(handle64, &h, sizeof h);
+  return 0;
+}
+int p0p_ipc_open(p0p_ctx* c, const void* handle64, uint64_t bytes, p0p_buf** out) {
+  P0P_ALIVE(c);
+  if (!handle64 || !out || !bytes) return fail(c, -1, "ipc_open: null pointer or empty range");
+  DeviceGuard g(c->device);
+  cudaIpcMemHandle_t h; memcpy(&h, handle64, sizeof h);
+  void* ptr = nullptr;
+  P0P_CUDA(c, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "ipc_open");
+  p0p_buf* b = new p0p_buf();
+  b->ptr = ptr; b->size = bytes; b->owned = false; b->ipc = true;
+  c->bufs.insert(b);
+  *out = b;
+  return 0;
+}
 int p0p_free(p0p_ctx* c, p0p_buf* b) {
   if (!c) return -1;
   if (!b || !c->bufs.count(b)) return 0;                                          // double free is a no-op (:113)
   DeviceGuard g(c->device);
   c->bufs.erase(b);
-  if (!b->owned) { delete b; return 0; }
+  if (!b->owned) { if (b->ipc) (void)cudaIpcCloseMemHandle(b->ptr); delete b; return 0; }
   c->alive -= b->size;
-  if (!c->status && c->alive + c->pooled + b->size <= pool_cap(c)) {              // :115-118
+  if (!b->plain && !c->status && c->alive + c->pooled + b->size <= pool_cap(c)) {  // :115-118
     b->seq = ++c->poolSeq;
     c->pool[b->size].push_back(b); c->pooled += b->size; c->pooledN++;
     return 0;

@@ -78,6 +78,10 @@ def gemm(gpu, a: dict) -> float:
     g.w_bytes = int(w.get("bytes") or 0)
     g.x_size = int(x["size"]) if x.get("size") is not None else 0
     g.y_size = int(y["size"]) if y.get("size") is not None else 0
+    peers = y.get("peers") or []          # not in the reference: the other ranks' copies of y (Gpu.ipcOpen), stored to as well
+    if len(peers) > 7: raise ValueError("gemm: at most 7 peer copies of y")
+    g.n_ypeers = len(peers)
+    for i, pb in enumerate(peers): g.y_peers[i] = pb.handle.value if hasattr(pb.handle, "value") else pb.handle
     fl_out = C.c_double()
     gpu._check(lib.p0p_gemm(gpu._h, C.byref(g), C.byref(fl_out)))
     return fl_out.value

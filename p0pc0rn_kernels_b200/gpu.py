@@ -116,9 +116,10 @@ class Gpu:
                     wgMem=self._desc["wgMem"], wgInv=self._desc["wgInv"], sms=self._desc["sms"], l2MB=self._desc["l2MB"])
 
     # ---------------------------------------------------------------- buffers (src/core/gpu.js:87-148)
-    def buffer(self, size, label="", usage=0) -> Buffer:
+    def buffer(self, size, label="", usage=0, shareable=False) -> Buffer:
+        """`shareable` (not in the reference): memory other processes can map (ipcExport / ipcOpen); never pooled."""
         h = C.c_void_p()
-        rc = lib.p0p_alloc(self._h, int(size), C.byref(h))
+        rc = (lib.p0p_alloc_shareable if shareable else lib.p0p_alloc)(self._h, int(size), C.byref(h))
         if rc == -2:
             raise GpuError(f"buffer {label} {size} B exceeds maxBufferSize")
         self._check(rc)
@@ -130,6 +131,23 @@ class Gpu:
         """Adopt device memory owned elsewhere (for instance a tensor of the host framework)."""
         h = C.c_void_p()
         self._check(lib.p0p_wrap(self._h, C.c_void_p(device_ptr), int(nbytes), C.byref(h)))
+        b = Buffer(self, h, int(nbytes), label)
+        self.bufs.add(b)
+        return b
+
+    def ipcExport(self, b: Buffer) -> bytes:
+        """Not in the reference: the 64-byte CUDA IPC handle of a buffer made by buffer() / upload(), for another process on
+        the node to map with ipcOpen."""
+        h = (C.c_ubyte * 64)()
+        self._check(lib.p0p_ipc_export(self._h, b.handle, C.cast(h, C.c_void_p)))
+        return bytes(h)
+
+    def ipcOpen(self, handle: bytes, nbytes: int, label="") -> Buffer:
+        """Not in the reference: map a buffer another process exported (another GPU of the node); usable as a peer copy of y
+        in gemm ({"y": {..., "peers": [...]}}).  free() unmaps it."""
+        raw = (C.c_ubyte * 64).from_buffer_copy(handle)
+        h = C.c_void_p()
+        self._check(lib.p0p_ipc_open(self._h, C.cast(raw, C.c_void_p), int(nbytes), C.byref(h)))
         b = Buffer(self, h, int(nbytes), label)
         self.bufs.add(b)
         return b

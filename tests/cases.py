@@ -57,7 +57,7 @@ def build(c: dict) -> dict:
     h = {"enc": enc, "M": M, "N": N, "K": K, "epi": epi, "xmode": xmode, "conv": conv, "wk0": wk0, "wr0": wr0, "wr1": wr1, "w_rows": w_rows,
          "w_cols": w_cols, "w_ld": w_ld, "W": np.ascontiguousarray(Wb), "Wd": Wd, "kernel": c.get("kernel"), "name": c.get("name", ""),
          "res": c.get("res", False), "store": c.get("store", False), "act": c.get("act", "silu"), "tile": c.get("tile"), "acc": c.get("acc"),
-         "w_off": c.get("w_off", 0), "x_off": c.get("x_off", 0), "y_off": c.get("y_off", 0)}
+         "w_off": c.get("w_off", 0), "x_off": c.get("x_off", 0), "y_off": c.get("y_off", 0), "peers": c.get("peers", 0)}
     # ---- X
     ldx = c.get("ldx", K); kx0 = c.get("kx0", 0)
     h["ldx"], h["kx0"] = ldx, kx0
@@ -173,9 +173,15 @@ def run_gpu(gpu, h: dict, gemm=None) -> np.ndarray:
                 bufs[k] = gpu.upload(data, k)
         y0 = h["Y0"] if not h["y_off"] else np.concatenate([np.full(h["y_off"], 0xAB, np.uint8), h["Y0"].view(np.uint8).reshape(-1)])
         bufs["Y"] = gpu.upload(y0, "Y")
-        fl = gemm(gpu, gemm_args(gpu, h, bufs))
+        args = gemm_args(gpu, h, bufs)
+        npeers = int(h.get("peers") or 0)
+        for q in range(npeers): bufs[f"YP{q}"] = gpu.upload(y0, f"Y peer {q}")          # same starting bytes as Y (read-modify-write epilogues)
+        if npeers: args["y"]["peers"] = [bufs[f"YP{q}"] for q in range(npeers)]
+        fl = gemm(gpu, args)
         assert fl == 2.0 * h["M"] * h["N"] * h["K"]
         raw = gpu.read(bufs["Y"], h["y_off"], h["Y0"].nbytes)
+        for q in range(npeers):
+            assert np.array_equal(gpu.read(bufs[f"YP{q}"], 0, y0.nbytes), gpu.read(bufs["Y"], 0, y0.nbytes)), f"peer copy {q} of y differs from y"
         if h["y_off"]:
             head = gpu.read(bufs["Y"], 0, h["y_off"])
             assert (head == 0xAB).all(), "bytes before y.off were written"

@@ -409,6 +409,30 @@ def test_decode_kernel(gpu, oracle, case):
         CS.check(got2, CS.run_oracle(h2), case["name"] + " (library's pick)")
 
 
+PEERS = [
+    dict(name="p decode M3 swiglu", enc="q4", M=3, N=256, K=512, epi="swiglu", peers=2),
+    dict(name="p decode M1 resadd", enc="q8", M=1, N=128, K=256, epi="resadd", peers=1),
+    dict(name="p umma rms+swiglu (row-wise stores)", enc="q4", M=100, N=512, K=512, xmode="rms", epi="swiglu", ldy=1024, ny0=256, peers=3),
+    dict(name="p umma resadd (fp32 rows)", enc="q4", M=300, N=256, K=512, epi="resadd", ldy=512, ny0=128, peers=2),
+    dict(name="p umma split-K heads", enc="q8", M=100, N=384, K=1536, xmode="lnmod", epi="heads", heads=dict(Ltot=128, Hq=1, Hkv=1, rowOff=7, eps=1e-6), peers=1),
+    dict(name="p umma scalar stores (odd ld)", enc="q4", M=40, N=100, K=256, w_rows=128, ldy=110, peers=7),
+]
+
+
+@pytest.mark.parametrize("case", PEERS, ids=lambda c: c["name"])
+def test_peer_copies_of_y(gpu, oracle, case):
+    """every store to y is repeated into the peer copies (here: other buffers of the same GPU), bit for bit, on both kernels"""
+    h = CS.build(dict(case))
+    got = CS.run_gpu(gpu, h)                  # run_gpu compares the peer buffers with y
+    CS.check(got, CS.run_oracle(h), case["name"])
+
+
+def test_peer_copies_refused_on_general_kernel(gpu):
+    h = CS.build(dict(name="p generic", enc="q4", M=2, N=128, K=96, peers=1))        # K % 64 != 0: only the general kernel takes it
+    with pytest.raises(ValueError, match="peer copies"):
+        CS.run_gpu(gpu, h)
+
+
 @pytest.mark.parametrize("enc,scale", [("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q4g32a.t64", "offset"), ("f16", 0.05)])
 @pytest.mark.parametrize("path", [0, 1])
 def test_dequant_bit_exact(gpu, oracle, enc, scale, path):
