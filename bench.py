@@ -496,6 +496,33 @@ def main():
     h2d = M * HID * 4
     e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms}
 
+    # ---- N > 1: one more block from the same tokens, checked.  Every rank's copy of the residual must hold the same bits (each
+    # rank wrote its columns into all copies), and rank 0 compares it with the same block run unsharded on its own GPU.
+    check = None
+    if world > 1:
+        x_t[: M * HID].copy_(torch.from_numpy(x_host[: M * HID])); torch.cuda.synchronize(); dist.barrier()
+        block(M, 0); torch.cuda.synchronize(); dist.barrier()
+        mine_sum = x_t[: M * HID].view(torch.int32).to(torch.int64).sum().reshape(1)
+        sums = [torch.zeros_like(mine_sum) for _ in range(world)]; dist.all_gather(sums, mine_sum)
+        identical = all(int(v.item()) == int(sums[0].item()) for v in sums)
+        rel = None
+        if rank == 0:
+            got = x_t[: M * HID].clone()
+            Wg = gpu.upload(synth_q4(2 * FF, HID, 1, P), "gate_up.full"); Wd = gpu.upload(synth_q4(HID, FF, 2, P), "down.full")
+            x2 = gpu.upload(x_host[: M * HID], "x.full"); h2 = gpu.buffer(M * FF * 2); x2_t = torch.as_tensor(DevView(x2, M * HID, "<f4"), device=dev)
+            P.rowstats(gpu, {"x": {"buf": x2}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
+            P.gemm(gpu, {"w": {"enc": "q4g32a.t64", "buf": Wg, "off": 0, "bytes": Wg._pf, "rows": 2 * FF, "cols": HID}, "x": {"buf": x2, "mode": "rms"}, "y": {"buf": h2, "ld": FF},
+                         "M": M, "N": 2 * FF, "K": HID, "wr0": 0, "wr1": FF, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}})
+            P.gemm(gpu, {"w": {"enc": "q4g32a.t64", "buf": Wd, "off": 0, "bytes": Wd._pf, "rows": HID, "cols": FF}, "x": {"buf": h2}, "y": {"buf": x2, "ld": HID},
+                         "M": M, "N": HID, "K": FF, "epi": "resadd"})
+            torch.cuda.synchronize()
+            rel = float(((got - x2_t).double().norm() / x2_t.double().norm()).item())
+            for bfr in (Wg, Wd, x2, h2): gpu.free(bfr)
+        dist.barrier()
+        check = {"replicas_bit_identical": identical, "rel_l2_vs_unsharded_on_rank0": rel}
+        if rank == 0 and (not identical or rel is None or rel > 1e-3):
+            print(f"MULTI-GPU CHECK FAILED: {check}", file=sys.stderr)
+
     # ---- decode-sized cases of the same config (HBM-bound): GB/s of the algorithmic bytes
     cases = []
     if not args.skip_cases:
@@ -540,7 +567,7 @@ def main():
                "config": {"workload": f"LLM MLP block q4, M={M} tokens: rowstats + gate/up K4096->2x14336 (rms, swiglu) + down K14336->4096 (resadd) (configs[1])",
                           "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + ("" if world == 1 else " + epilogues store each rank's columns into every rank's buffers (peer stores), one-element all-reduce as barrier" if fused else " + NCCL all-gather of hidden and output"),
                           "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)"},
-               "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
+               "e2e": e2e, "multi_gpu_check": check, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
                "GB/s": block_bytes(M) / (ms * 1e-3) / 1e9}
         print(json.dumps(out), flush=True)
     # leave without tearing down: CUDA graphs that hold NCCL kernels and the process group do not unwind in a safe

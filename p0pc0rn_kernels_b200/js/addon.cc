@@ -103,6 +103,13 @@ napi_value Gemm(napi_env env, napi_callback_info info) {
   g.ev = bufp(env, o, "ev"); g.bv = bufp(env, o, "bv"); g.rp = bufp(env, o, "rp"); g.gt = bufp(env, o, "gt");
   g.x_off = (uint64_t)f64(env, o, "x_off"); g.w_off = (uint64_t)f64(env, o, "w_off"); g.y_off = (uint64_t)f64(env, o, "y_off");
   g.w_bytes = (uint64_t)f64(env, o, "w_bytes"); g.x_size = (uint64_t)f64(env, o, "x_size"); g.y_size = (uint64_t)f64(env, o, "y_size");
+  {   // y.peers: externals of buffers opened with ipcOpen (multi-GPU extension; absent in the reference's argument object)
+    bool has = false; napi_has_named_property(env, o, "y_peers", &has);
+    if (has) {
+      napi_value arr; napi_get_named_property(env, o, "y_peers", &arr); uint32_t n = 0; napi_get_array_length(env, arr, &n);
+      for (uint32_t i = 0; i < n && i < 7u; i++) { napi_value e; napi_get_element(env, arr, i, &e); g.y_peers[i] = unwrap<p0p_buf>(env, e); g.n_ypeers = i + 1u; }
+    }
+  }
   double flops = 0; int rc = p0p_gemm(c, &g, &flops); if (rc) return throw_ctx(env, c, rc);
   napi_value r; napi_create_double(env, flops, &r); return r;
 }
