@@ -32,7 +32,8 @@
 
 namespace p0p {
 
-constexpr int U_THREADS = 480;           // 15 warps
+constexpr int U_NG = 3;                  // dequantisation groups of four warps that take the k-steps in turn
+constexpr int U_THREADS = (6 + 4 * U_NG + 1) * 32;
 constexpr int U_NQ_MAX = 8;              // most stages of quantised records
 constexpr int U_A_BYTES = 128 * 128;     // one weight operand stage: 128 rows x 64 fp16
 constexpr int U_EPI_TB = 16;             // tokens per epilogue pass
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       mbar_init(full + 8u * s, ENC == P0P_ENC_F16 ? 1u : 5u);     // the producer's expect_tx arrival (+ the four warps of a dequant group)
       mbar_init(empty + 8u * s, 1u);
     }
-    for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, 8u); }
+    for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, 4u * U_NG); }
     for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
     fence_mbar_init();
   }
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         }
       }
     }
-  } else if (warp == 14) {
+  } else if (warp == 6u + 4u * U_NG) {
     // ================================================================= producer of the quantised records: runs ahead of
     // everything else by NQ stages (its only wait is for a free record stage)
     if (ENC != P0P_ENC_F16 && lane == 0) {
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
     }
-  } else if (ENC != P0P_ENC_F16 && warp < 14) {
+  } else if (ENC != P0P_ENC_F16 && warp < 6u + 4u * U_NG) {
     // ================================================================= dequantisation: codes -> swizzled fp16 operand rows.
     // Two groups of four warps take alternate k-steps; a thread converts one whole operand row (64 k) of a step.
     const uint32_t dw = warp - 6u, grp = dw >> 2, r = (warp & 3u) * 32u + lane;      // a warp reaches the tensor-memory lanes 32 * (warp % 4) .. + 31
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == ke - 1u;
         if (turn == grp) {
           // the record stage is awaited at this group's first use of it only (sub 0 or 1: the groups alternate)
-          if ((sub < 2u && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
+          if ((sub < (uint32_t)U_NG && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
           const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + sub * UQ<ENC>::RB;
           const uint32_t dst = a_st + ar.s * U_A_BYTES + r * 128u;
           if (ENC == P0P_ENC_Q4) {
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         }
         // every warp walks every k-step, so it releases each record stage exactly once, after its own last use of it
         if (last_sub) { __syncwarp(); if (lane == 0) mbar_arrive(wq_empty + 8u * qr.s); qr.next(); sub = 0; } else sub++;
-        ar.next(); turn ^= 1u;
+        ar.next(); if (++turn == (uint32_t)U_NG) turn = 0u;
       }
     }
   }
