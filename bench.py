@@ -127,7 +127,7 @@ def run_reference(args, rank):
         os._exit(0)
     import oracle as O
     O.build()
-    thr = O.max_threads()
+    thr = max(O.max_threads(), len(os.sched_getaffinity(0)))       # torchrun pins OMP_NUM_THREADS to 1: the host's cores are still there
     rows, gu, dn = 64, 1024, 512
     for _ in range(args.warmup): cpu_sample(1, 256, 128, thr)
     t = 0.0; fl = 0.0
@@ -555,7 +555,7 @@ def main():
         cpu = None
         if world == 1:                       # the CPU baseline is a single-GPU-run figure (and torchrun pins its ranks to one thread)
             import oracle as O
-            O.build(); thr = O.max_threads()
+            O.build(); thr = max(O.max_threads(), len(os.sched_getaffinity(0)))
             cpu_sample(1, 256, 128, thr)
             cm = min(M, 512)
             f, d = cpu_sample(cm, FF // 2, HID // 2, thr, reps=4)

@@ -1,11 +1,11 @@
-// Decode-sized multiply (M <= 16 tokens, q4 / q8 weights): the call is bound by streaming the weights out of
-// HBM once, so the kernel is built around that stream.
+// Decode-sized multiply (up to 16 tokens, the library's own choice up to 8; q4 / q8 weights): the call is bound by
+// streaming the weights out of HBM once, so the kernel is built around that stream.
 //
 //   stage 1  k_decode_stream   The (64-row tile) x (k-block) units of the weight are spread evenly over a grid of
 //            about three blocks per SM.  In each block one producer lane moves whole records from global to
 //            shared memory with bulk asynchronous copies (cp.async.bulk, mbarrier-tracked, a ring of stages);
-//            four consumer warps each own 16 rows of the tile.  Codes go to the tensor cores WITHOUT being
-//            dequantised: a 4-bit code q becomes the fp16 bit pattern 0x6400|q (= 1024+q) or 0x6400|q<<4
+//            eight consumer warps: four row groups of 16 rows, two warps each that split a stage's records.
+//            Codes go to the tensor cores WITHOUT being dequantised: a 4-bit code q becomes the fp16 bit pattern 0x6400|q (= 1024+q) or 0x6400|q<<4
 //            (= 1024+16q) by one lop3, an 8-bit code the pattern 0x6400|(q+128), and mma.sync.m16n8k16
 //            (weights = A, tokens = B, fp32 accumulate) sums code*x over one group.  The group's scale and
 //            minimum are applied to the fp32 sum afterwards:  y += s * (acc - C) + mn * Sx,  where

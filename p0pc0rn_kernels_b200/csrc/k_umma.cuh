@@ -1,23 +1,31 @@
-// The tensor-core kernel for M > 16: tcgen05.mma with fp32 accumulators in tensor memory (TMEM).
+// The tensor-core kernel: tcgen05.mma with fp32 accumulators in tensor memory (TMEM).  Serves 9 tokens and more, every
+// weight encoding, the plain / RMSNorm / LayerNorm+modulation prologues and the 3x3x3 conv3 mode, every epilogue.
 //
 // Orientation.  The 128 lanes of an accumulator are 128 weight rows (= output columns n) and its columns
 // are tokens:  D[n, m] = sum_k W[n, k] * X'[m, k].  Weights are the A operand (UMMA M = 128), tokens the B
-// operand (UMMA N = BT = 16..256 tokens), both K-major fp16 tiles of 64 k in shared memory with the 128-byte
-// swizzle.  A small M therefore costs a narrow instruction instead of a mostly empty 128-row tile, and every
-// epilogue thread owns one output column, which is what the fused epilogues need (epilogue.cuh).
+// operand (UMMA N = tokens), K-major fp16 tiles of 64 k.  A small M therefore costs a narrow instruction instead
+// of a mostly empty 128-row tile, and every epilogue thread owns one output column, which is what the fused
+// epilogues need (epilogue.cuh).
 //
-// Pipeline of one block (persistent over output tiles, one block per SM), by warp:
-//   warp 0        producer   TMA tensor-map loads of the token tile (and of fp16 weights), bulk copies of the
-//                            quantised records (two 64-row record tiles x 64 k per step), all mbarrier-tracked
-//   warps 6..13   dequant    codes -> fp16 tile values f16(q*s+mn) / f16(q*s), bit-exact (packed HFMA2 path with a
-//                            per-warp exactness test and an fp32 fallback), written in the swizzled operand layout
-//   warp 1        MMA        one lane issues 4 x tcgen05.mma (k = 16 each) per step and commits to the stage's
-//                            "free" barrier; after the last step commits to the accumulator's "full" barrier
-//   warps 2..5    epilogue   tcgen05.ld of 16 tokens at a time, fused epilogue, global stores; two accumulators
-//                            (2 x 256 TMEM columns) let the next tile's multiply overlap
-// gate|up (swiglu) tiles interleave gate and up rows in the A tile, so that (gate, up) of one output sit in
-// adjacent lanes.  RMSNorm / LayerNorm+modulation prologues are applied by a one-pass kernel into an fp16
-// scratch copy of the tokens (the same token tile would otherwise be re-normalised by every column tile).
+// Pipeline of one block (persistent over work units, one block per SM), by warp:
+//   warp 0          producer   TMA tensor-map loads of the token tile (2-D map of the tokens, or 4-D boxes of the conv3
+//                              clip) and of fp16 weight tiles, mbarrier-tracked
+//   warp 1          MMA        the whole warp walks the loop, one elected lane issues 4 x tcgen05.mma (k = 16 each, x 2
+//                              for tiles wider than 256 tokens) per step and commits to the stage's "free" barrier; after
+//                              the unit's last step it commits to the accumulator's "full" barrier
+//   warps 2..5      epilogue   tcgen05.ld of 16 tokens at a time, fused epilogue (or the raw partial sums of a split-K
+//                              unit), row-wise 16-byte stores
+//   warps 6..       dequant    U_NG groups of four warps take the k-steps in turn: codes -> fp16 tile values f16(q*s+mn) /
+//                              f16(q*s), bit-exact (packed HFMA2 path with a per-warp exactness test and an fp32 fallback),
+//                              written straight into tensor memory (tcgen05.st): the multiply takes A from there
+//   last warp       records    bulk copies of the quantised records (two 64-row record tiles x up to 256 k per copy pair)
+// Tensor memory: 384 accumulator columns + four 32-column operand stages (quantised weights), or 512 accumulator columns
+// (fp16 weights, both operands in shared memory).  The accumulator columns hold two tiles of up to 192 tokens (the next
+// tile's multiply overlaps the epilogue), or one tile of up to 384, or 2 / 4 accumulators of one narrow tile that take the
+// 16-k multiplies in turn (see launch_umma for why).  gate|up (swiglu) tiles interleave gate and up rows in the A tile, so
+// that (gate, up) of one output sit in adjacent lanes.  RMSNorm / LayerNorm+modulation prologues are applied by a one-pass
+// kernel into an fp16 scratch copy of the tokens (the same token tile would otherwise be re-normalised by every column
+// tile).  Few output columns: the k loop is split into units whose partial sums k_umma_finish adds (split-K).
 // Every mbarrier wait is bounded (sync.cuh); on a time-out the block reports a code and winds down.
 #pragma once
 #include <cuda.h>
@@ -32,7 +40,7 @@
 
 namespace p0p {
 
-constexpr int U_NG = 3;                  // dequantisation groups of four warps that take the k-steps in turn
+constexpr int U_NG = 2;                  // dequantisation groups of four warps that take the k-steps in turn
 constexpr int U_THREADS = (6 + 4 * U_NG + 1) * 32;
 constexpr int U_NQ_MAX = 8;              // most stages of quantised records
 constexpr int U_A_BYTES = 128 * 128;     // one weight operand stage: 128 rows x 64 fp16
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     }
   } else if (ENC != P0P_ENC_F16 && warp < 6u + 4u * U_NG) {
     // ================================================================= dequantisation: codes -> swizzled fp16 operand rows.
-    // Two groups of four warps take alternate k-steps; a thread converts one whole operand row (64 k) of a step.
+    // The groups of four warps take the k-steps in turn; a thread converts one whole operand row (64 k) of a step.
     const uint32_t dw = warp - 6u, grp = dw >> 2, r = (warp & 3u) * 32u + lane;      // a warp reaches the tensor-memory lanes 32 * (warp % 4) .. + 31
     const uint32_t tsel = swiglu ? (r & 1u) : (r >> 6), rr = swiglu ? (r >> 1) : (r & 63u);
     const uint32_t rsw = r & 7u;
@@ -279,7 +287,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       for (uint32_t ks = kb; ks < ke; ks++) {
         const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == ke - 1u;
         if (turn == grp) {
-          // the record stage is awaited at this group's first use of it only (sub 0 or 1: the groups alternate)
+          // the record stage is awaited at this group's first use of it only (its first U_NG k-steps: the groups take turns)
           if ((sub < (uint32_t)U_NG && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
           const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + sub * UQ<ENC>::RB;
           const uint32_t dst = a_st + ar.s * U_A_BYTES + r * 128u;

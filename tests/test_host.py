@@ -34,6 +34,22 @@ def test_library_exports_every_declared_symbol(P):
     assert L.p0p_abi_version() == 1
 
 
+def test_argument_block_layout_matches_header(P, tmp_path):
+    """the ctypes transcription of p0p_gemm_args has the header's size and field offsets (checked by compiling the header with gcc)"""
+    import ctypes as C, subprocess, shutil
+    if not shutil.which("gcc"): pytest.skip("no gcc")
+    from p0pc0rn_kernels_b200._lib import GemmArgs
+    fields = ["struct_size", "M", "eps", "force_kernel", "x", "gt", "x_off", "y_size", "n_ypeers", "y_peers"]
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "p0p.h"\nint main(void){printf("%zu", sizeof(p0p_gemm_args));'
+                   + "".join(f'printf(" %zu", offsetof(p0p_gemm_args, {f}));' for f in fields) + "return 0;}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    assert got[0] == C.sizeof(GemmArgs)
+    assert got[1:] == [getattr(GemmArgs, f).offset for f in fields]
+
+
 def test_no_gpu_fails_loudly(P):
     import torch
     if torch.cuda.is_available():
