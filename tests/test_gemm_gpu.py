@@ -523,3 +523,25 @@ def test_buffers(gpu):
     gpu.free(b)
     with pytest.raises(ValueError):
         gpu.read(b.__class__(gpu, b.handle, 16), 0, 16)
+
+
+def test_shareable_buffers_and_read_into(gpu):
+    """the two buffer extensions: memory other processes can map (zeroed, never pooled, exportable) and reads into the caller's array"""
+    a = gpu.buffer(1000, "shared", shareable=True)
+    assert a._pf == 1008 and not gpu.read(a).any()
+    gpu.upload(np.arange(1000, dtype=np.uint8), "", a, 0)
+    out = np.zeros(1000, np.uint8)
+    got = gpu.read(a, 0, 1000, out=out)
+    assert got is out and out.tolist() == [i % 256 for i in range(1000)]
+    assert len(gpu.ipcExport(a)) == 64
+    b = gpu.buffer(1000)
+    with pytest.raises(ValueError, match="shareable"):
+        gpu.ipcExport(b)                                  # the stream-ordered pool's memory has no handle
+    with pytest.raises(ValueError):
+        gpu.read(a, 0, 1000, out=np.zeros(10, np.uint8))
+    s0 = gpu.poolStats()
+    gpu.free(a); gpu.free(b)
+    c = gpu.buffer(1000, "shared", shareable=True)        # a new allocation, cleared
+    assert not gpu.read(c).any()
+    gpu.free(c)
+    assert gpu.poolStats()["alive"] <= s0["alive"]
