@@ -173,6 +173,19 @@ int p0p_alloc_shareable(p0p_ctx* ctx, uint64_t bytes, p0p_buf** out);
 int p0p_ipc_export(p0p_ctx* ctx, const p0p_buf* buf, void* handle64);
 int p0p_ipc_open(p0p_ctx* ctx, const void* handle64, uint64_t bytes, p0p_buf** out);
 
+/* attention, head_dim 128 (src/ops/attention.js:168-193; argument object types/index.d.ts `AttentionArgs`): the step after the
+ * 'heads' projection.  Q [Hq][Lq][128] f16, K / V [Hkv][Lk][128] f16 head-major, O [Lq][ldo] f16 token-major at column h*128.
+ * mode 0 none, 1 causal + valid length (key j visible to query i iff j <= min(i, nvalid-1)), 2 valid length (j < nvalid);
+ * Hkv 0 = Hq, Lk 0 = Lq, ldo 0 = Hq*128, scale 0 = 1/sqrt(128), nvalid 0 = Lk.  *flops = 4*Lq*Lk*128*Hq (:192). */
+typedef struct p0p_attn_args {
+  uint32_t struct_size;
+  uint32_t Hq, Hkv, Lq, Lk, ldo, mode, nvalid;
+  float scale;
+  p0p_buf *q, *k, *v, *o;
+  uint64_t q_off, k_off, v_off, o_off;   /* bytes */
+} p0p_attn_args;
+int p0p_attention(p0p_ctx* ctx, const p0p_attn_args* args, double* flops);
+
 /* Debug op: writes the fp16 tile values the kernels feed to the multiply, rows [r0, r0+nr) x all w_cols
  * columns, row-major into `out` (fp16).  path 0 = the fp32-FMA conversion, 1 = the packed half2 conversion
  * the tensor-core kernels use.  Both must equal f16(q*s+min) / f16(q*s) of docs/FORMAT.md bit for bit. */

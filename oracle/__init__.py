@@ -160,6 +160,17 @@ def rowstats(X, rows: int, cols: int, ld: int | None = None, rms: bool = False, 
     lib().orc_rowstats(_p(X), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(ld or cols), C.c_int(1 if rms else 0), C.c_float(eps), _p(ST)); return ST
 
 
+def cpu_attn(Q, Kt, V, *, Hq: int, Hkv: int | None = None, Lq: int, Lk: int | None = None, D: int = 128, mode: int = 0, nvalid: int | None = None,
+             scale: float | None = None, cap: float = 0.0, threads: int = 0) -> np.ndarray:
+    """cpuAttn of test/kernels.test.js:32-48 -> O float32 [Lq][Hq*D]"""
+    Hkv = Hkv or Hq; Lk = Lk or Lq; nvalid = nvalid or Lk
+    Q, Kt, V = _f32(Q).ravel(), _f32(Kt).ravel(), _f32(V).ravel()
+    O_ = np.empty(Lq * Hq * D, np.float32)
+    lib().orc_cpu_attn(_p(Q), _p(Kt), _p(V), _p(O_), C.c_uint32(Hq), C.c_uint32(Hkv), C.c_uint32(Lq), C.c_uint32(Lk), C.c_uint32(D), C.c_uint32(mode),
+                       C.c_uint32(nvalid), C.c_double(scale if scale is not None else 1.0 / np.sqrt(D)), C.c_double(cap), C.c_int(threads or max_threads()))
+    return O_
+
+
 def max_threads() -> int:
     return int(lib().orc_max_threads())
 

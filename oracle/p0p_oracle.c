@@ -229,6 +229,41 @@ API void orc_dequant(int enc, const uint8_t* W, uint32_t r0, uint32_t nr, uint32
  * The reference test-suite's CPU multiplications — test/kernels.test.js:29, 52-65, 16-21
  * ---------------------------------------------------------------------------------------------- */
 
+/* cpuAttn (test/kernels.test.js:32-48): Q [Hq][Lq][D], K / V [Hkv][Lk][D] -> O [Lq][Hq*D] (token-major).  Scores are
+ * accumulated in double and stored to a float array (the reference's Float32Array s), the maximum is tracked in double,
+ * exp(s - mx) is stored as float, the sum and the PV products run in double, O is stored as float.  cap > 0: soft cap. */
+API void orc_cpu_attn(const float* Q, const float* Kt, const float* V, float* O, uint32_t Hq, uint32_t Hkv, uint32_t Lq, uint32_t Lk, uint32_t D,
+                      uint32_t mode, uint32_t nvalid, double scale, double cap, int threads) {
+  const uint32_t grp = Hq / Hkv;
+  (void)threads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+  for (uint32_t h = 0; h < Hq; h++)
+    for (uint32_t i = 0; i < Lq; i++) {
+      const uint32_t kh = h / grp;
+      float* s = (float*)malloc((size_t)Lk * sizeof(float));
+      double mx = -INFINITY;
+      for (uint32_t j = 0; j < Lk; j++) {
+        const uint32_t lim = i < nvalid - 1u ? i : nvalid - 1u;
+        const int vis = mode == 1u ? j <= lim : mode == 2u ? j < nvalid : 1;
+        if (!vis) { s[j] = -INFINITY; continue; }
+        double a = 0.0;
+        for (uint32_t d = 0; d < D; d++) a += (double)Q[((size_t)h * Lq + i) * D + d] * (double)Kt[((size_t)kh * Lk + j) * D + d];
+        a *= scale;
+        if (cap > 0.0) a = cap * tanh(a / cap);
+        s[j] = (float)a;
+        if (a > mx) mx = a;
+      }
+      double sum = 0.0;
+      for (uint32_t j = 0; j < Lk; j++) { s[j] = isinf(s[j]) && s[j] < 0 ? 0.0f : (float)exp((double)s[j] - mx); sum += (double)s[j]; }
+      for (uint32_t d = 0; d < D; d++) {
+        double a = 0.0;
+        for (uint32_t j = 0; j < Lk; j++) a += (double)s[j] * (double)V[((size_t)kh * Lk + j) * D + d];
+        O[(size_t)i * Hq * D + (size_t)h * D + d] = (float)(a / sum);
+      }
+      free(s);
+    }
+}
+
 /* cpuGemm: float64 accumulate, float32 store (test/kernels.test.js:29).  threads<=1: the single-threaded
  * loop of the reference; otherwise OpenMP over rows. */
 API void orc_cpu_gemm(const float* X, const float* W, float* Y, uint32_t M, uint32_t N, uint32_t K, int threads) {

@@ -2,6 +2,7 @@
 
 The names exported here are the reference's (src/index.js) for the gemm path and the model I/O either side of it.
 The native library must be built (``python p0pc0rn_kernels_b200/build.py``); there is no CPU fallback."""
+from .attention import attention
 from .convert import ALIGN, convert, convertSafetensors, encodedBytes, writeSafetensors
 from .encode import (MANIFEST_FORMAT, chooseEncoding, dtypeBytes, encodeRows, matrixOf, packF16, packF32, packQ4, packQ8, reorderConvRows,
                      safetensorsHeader, safetensorsList, tileBytes, toFloat32)

@@ -16,7 +16,7 @@ SYMBOLS = [
     "p0p_write", "p0p_read", "p0p_clear", "p0p_copy", "p0p_sync", "p0p_host_alloc", "p0p_host_free",
     "p0p_capture_begin", "p0p_capture_end", "p0p_graph_launch", "p0p_graph_free",
     "p0p_decode_q4_static", "p0p_alloc_shareable", "p0p_ipc_export", "p0p_ipc_open",
-    "p0p_gemm", "p0p_last_kernel", "p0p_launch_count", "p0p_dequant", "p0p_rowstats",
+    "p0p_gemm", "p0p_attention", "p0p_last_kernel", "p0p_launch_count", "p0p_dequant", "p0p_rowstats",
     "p0p_f2h", "p0p_h2f", "p0p_to_f16", "p0p_from_f16", "p0p_pack_q4", "p0p_pack_q8", "p0p_reorder_conv_rows",
     "p0p_encoded_bytes", "p0p_shard_rows", "p0p_abi_version",
 ]
@@ -44,6 +44,11 @@ class GemmArgs(C.Structure):
                 + [("n_ypeers", C.c_uint32), ("reserved0", C.c_uint32), ("y_peers", C.c_void_p * 7)])
 
 
+class AttnArgs(C.Structure):
+    _fields_ = ([(n, C.c_uint32) for n in ("struct_size", "Hq", "Hkv", "Lq", "Lk", "ldo", "mode", "nvalid")] + [("scale", C.c_float)]
+                + [(n, C.c_void_p) for n in ("q", "k", "v", "o")] + [(n, C.c_uint64) for n in ("q_off", "k_off", "v_off", "o_off")])
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(f"{LIB_PATH} is missing: build it with `python p0pc0rn_kernels_b200/build.py` (needs nvcc); there is no CPU fallback")
@@ -60,7 +65,7 @@ def _load():
         "p0p_capture_begin": (i, [vp]), "p0p_capture_end": (i, [vp, C.POINTER(vp)]), "p0p_graph_launch": (i, [vp, vp]), "p0p_graph_free": (i, [vp, vp]),
         "p0p_decode_q4_static": (i, [i, vp, vp, vp, vp, u32, u32, u32, C.c_char_p, C.c_size_t]),
         "p0p_alloc_shareable": (i, [vp, u64, C.POINTER(vp)]), "p0p_ipc_export": (i, [vp, vp, vp]), "p0p_ipc_open": (i, [vp, vp, u64, C.POINTER(vp)]),
-        "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]),
+        "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_attention": (i, [vp, C.POINTER(AttnArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]),
         "p0p_dequant": (i, [vp, u32, vp, u64, u32, u32, u32, u32, u32, vp, u64]),
         "p0p_rowstats": (i, [vp, vp, u64, u32, u32, u32, u32, u32, C.c_float, vp, u32]),
         "p0p_f2h": (C.c_uint16, [C.c_float]), "p0p_h2f": (C.c_float, [C.c_uint16]),

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libp0p.so")
-SOURCES = ["runtime.cu", "gemm.cu", "noalloc.cu", "host_codec.cpp"]
+SOURCES = ["runtime.cu", "gemm.cu", "attn.cu", "noalloc.cu", "host_codec.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC,-fvisibility=default,-ffp-contract=off", "-Xptxas", "-v"]
 
