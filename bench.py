@@ -247,6 +247,17 @@ def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
                               "TFLOP/s": fl / (ms * 1e-3) / 1e12, "GB/s": by / (ms * 1e-3) / 1e9, "frac_tensor": fl / (ms * 1e-3) / 1e12 / pk["tensor"]}), flush=True)
             for b in Ws + [x, st, pv, ev, rp, y]: gpu.free(b)
             gpu.drainPool()
+        elif name == "attention":
+            # the attention that consumes the DiT projection's heads: 24 heads of 128 over 3600 tokens, no mask
+            H, L = 24, 3600
+            q = gpu.upload(P.toF16((rs.standard_normal(H * L * 128) * 0.5).astype(np.float32))); k = gpu.upload(P.toF16((rs.standard_normal(H * L * 128) * 0.5).astype(np.float32)))
+            v = gpu.upload(P.toF16(rs.standard_normal(H * L * 128).astype(np.float32))); o = gpu.buffer(L * H * 128 * 2)
+            def call(): P.attention(gpu, {"q": {"buf": q}, "k": {"buf": k}, "v": {"buf": v}, "o": {"buf": o}, "Lq": L, "Lk": L, "Hq": H, "Hkv": H, "mode": 0})
+            ms = graph_time(call, max(3, min(args.steps, 20)))
+            fl = 4.0 * L * L * 128 * H
+            print(json.dumps({"config": "attention after dit_qkv (24 heads x 3600 tokens x 128, no mask)", "family": "mma.sync flash attention", "ms": ms,
+                              "TFLOP/s": fl / (ms * 1e-3) / 1e12, "frac_tensor": fl / (ms * 1e-3) / 1e12 / pk["tensor"]}), flush=True)
+            for b in (q, k, v, o): gpu.free(b)
         elif name == "conv3":
             T, Hh, Ww, C, N = 13, 92, 160, 128, 128
             K = 27 * C; fx = Hh * Ww * C; fy = Hh * Ww * N
@@ -300,7 +311,7 @@ def main():
     ap.add_argument("--skip-cases", action="store_true", help="only the headline (for profiler captures)")
     ap.add_argument("--kernel", default=None, help="force a kernel family (generic | decode | umma)")
     ap.add_argument("--shape", default=None, help="enc:M:N:K[,enc:M:N:K...]  time plain GEMMs of these shapes instead of the block (q4|q8|f16)")
-    ap.add_argument("--config", default=None, help="dit_qkv | conv3 [,…]: time the baseline's other single-GPU configurations instead of the block")
+    ap.add_argument("--config", default=None, help="dit_qkv | conv3 | attention [,…]: time the baseline's other single-GPU configurations instead of the block")
     ap.add_argument("--sweep", action="store_true", help="the large-shape sweep of the baseline's configs (q4/q8, M in 1..8192, four (N,K))")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local = int(os.environ.get("LOCAL_RANK", 0))
