@@ -58,9 +58,10 @@ struct UmmaP {
   uint32_t n_tiles, m_tiles;
   uint32_t G;           // token tiles per group of the tile order (tile_coords)
   uint32_t cvR;         // conv3: image rows per token tile (tile = cvR x Wo output positions of one frame)
-  uint32_t S, ks_per;   // split-K: units = tiles x S, each over ks_per k-steps; S > 1 leaves fp32 partial sums in sk_part
-  float* sk_part;       // [S][m_tiles * BT][sk_ld] partial sums (k_umma_finish adds them and applies the epilogue)
-  uint32_t sk_ld;
+  uint32_t T0, S, ks_per;   // split-K: the first T0 tiles (in tile order) are whole units; each of the rest is S units of ks_per
+                            // k-steps whose fp32 partial sums go to sk_part.  T0 = all tiles: no split; T0 = 0: every tile split;
+                            // in between: only the tiles of the last, nearly empty round are split over the idle SMs
+  float* sk_part;           // [S][tiles - T0][BT][128] partial sums (k_umma_finish adds them and applies the epilogue)
   int* status;
 };
 
@@ -84,6 +85,18 @@ __device__ __forceinline__ uint16_t u_lds16(uint32_t a) { uint16_t v; asm volati
 __device__ __forceinline__ void tile_coords(const UmmaP& u, uint32_t tile, uint32_t& nt, uint32_t& mt) {
   const uint32_t per = u.G * u.n_tiles, g = tile / per, local = tile - g * per, gsz = min(u.G, u.m_tiles - g * u.G);
   nt = local / gsz; mt = g * u.G + (local - nt * gsz);
+}
+
+// work unit -> tile and k range
+struct UnitOf { uint32_t tile, sp, kb, ke; bool split; };
+__device__ __forceinline__ UnitOf unit_of(const UmmaP& u, uint32_t unit, uint32_t tiles, uint32_t KS) {
+  UnitOf r;
+  if (unit < u.T0) { r.tile = unit; r.sp = 0u; r.kb = 0u; r.ke = KS; r.split = false; }
+  else {
+    const uint32_t tail = tiles - u.T0, v = unit - u.T0;
+    r.sp = v / tail; r.tile = u.T0 + (v - r.sp * tail); r.kb = r.sp * u.ks_per; r.ke = min(KS, r.kb + u.ks_per); r.split = true;
+  }
+  return r;
 }
 
 // ring position that wraps without division
@@ -135,7 +148,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gbase + (tmem_slot - base));
 
-  const uint32_t tiles = u.n_tiles * u.m_tiles, KS = p.K / 64u, units = tiles * u.S;
+  const uint32_t tiles = u.n_tiles * u.m_tiles, KS = p.K / 64u, units = u.T0 + (tiles - u.T0) * u.S;
   const bool swiglu = p.epi == P0P_EPI_SWIGLU;
 
   if (warp == 0) {
@@ -144,7 +157,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       Ring r(NS);
       bool ok = true;
       for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-        const uint32_t tile = unit % tiles, kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
+        const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t tile = un.tile, kb = un.kb, ke = un.ke;
         uint32_t nt, mt; tile_coords(u, tile, nt, mt);
         for (uint32_t ks = kb; ks < ke; ks++, r.next()) {
           if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
@@ -174,7 +187,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       bool ok = true;
       const uint32_t last = (p.Nw >> 6) - 1u;                  // record tiles past the weight's end do not exist: their columns are never stored
       for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-        const uint32_t tile = unit % tiles, kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
+        const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t tile = un.tile, kb = un.kb, ke = un.ke;
         uint32_t nt, mt; tile_coords(u, tile, nt, mt);
         uint32_t trow[2];
         if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
@@ -200,7 +213,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     uint32_t tl = 0;
     bool ok = true;
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x, tl++) {
-      const uint32_t kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
+      const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t kb = un.kb, ke = un.ke;
       const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
       if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8u * buf, par ^ 1u, u.status, 203, 100u))) { ok = false; break; }
       tc_fence_after();
@@ -240,7 +253,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     bool ok = true;
     const bool vec = epilogue_vec_ok(p);
     for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x, tl++) {
-      const uint32_t tile = unit % tiles, sp = unit / tiles;
+      const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t tile = un.tile, sp = un.sp;
       uint32_t nt, mt; tile_coords(u, tile, nt, mt);
       const uint32_t buf = two_acc ? tl & 1u : 0u, par = two_acc ? (tl >> 1) & 1u : tl & 1u;
       if (ok && !mbar_wait(acc_full + 8u * buf, par, u.status, 206, 1000u)) ok = false;
@@ -260,11 +273,11 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
           for (int j = 0; j < U_EPI_TB; j++) acc[j] += ok ? __uint_as_float(r[j]) : 0.0f;
         }
         if (ch + 1u < nchunks) tmem_ld16(t0 + (ch + 1u) * U_EPI_TB, r);      // the next pass's accumulators load behind this pass's work
-        if (u.S > 1u) {
+        if (un.split) {
           // split-K: this unit's partial sums, fp32, to its own slab; a warp's store covers 128 bytes of a row
-          float* dst = u.sk_part + ((size_t)sp * u.m_tiles * BT + m0 + ch * U_EPI_TB) * u.sk_ld + nt * 128u + c;
+          float* dst = u.sk_part + (((size_t)sp * (tiles - u.T0) + (tile - u.T0)) * BT + ch * U_EPI_TB) * 128u + c;
 #pragma unroll
-          for (int j = 0; j < U_EPI_TB; j++) dst[(size_t)j * u.sk_ld] = acc[j];
+          for (int j = 0; j < U_EPI_TB; j++) dst[(size_t)j * 128u] = acc[j];
         } else epilogue_cols<U_EPI_TB>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
       }
       tc_fence_before();
@@ -283,7 +296,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     uint32_t sub = 0, turn = 0;
     bool ok = true;
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-      const uint32_t kb = (unit / tiles) * u.ks_per, ke = min(KS, kb + u.ks_per);
+      const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t kb = un.kb, ke = un.ke;
       for (uint32_t ks = kb; ks < ke; ks++) {
         const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == ke - 1u;
         if (turn == grp) {
@@ -362,23 +375,27 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, U_TMEM_COLS); }
 }
 
-// ---- split-K second stage: the S partial sums of 16 tokens x 128 columns are added in split order (deterministic) and
-// the fused epilogue runs on the sum.  grid = (column blocks, 16-token groups), 128 threads.
-__global__ void __launch_bounds__(128) k_umma_finish(const KP p, const float* __restrict__ part, uint32_t S, uint32_t mpad, uint32_t ld) {
+// ---- split-K second stage: the S partial sums of 16 tokens x 128 columns of a split tile are added in split order
+// (deterministic) and the fused epilogue runs on the sum.  grid = (split tiles, 16-token groups of a tile), 128 threads.
+__global__ void __launch_bounds__(128) k_umma_finish(const UmmaP u) {
   __shared__ __align__(16) float sh[2 * U_EPI_TB * 132];
-  const uint32_t c = threadIdx.x, nB = blockIdx.x * 128u, m0 = blockIdx.y * U_EPI_TB;
+  const KP& p = u.p;
+  const uint32_t tiles = u.n_tiles * u.m_tiles, tail = tiles - u.T0, t = blockIdx.x, c = threadIdx.x;
+  uint32_t nt, mt; tile_coords(u, u.T0 + t, nt, mt);
+  const uint32_t r0 = blockIdx.y * U_EPI_TB, m0 = mt * u.BT + r0;
+  if (m0 >= p.M) return;
   float acc[U_EPI_TB];
 #pragma unroll
   for (int j = 0; j < U_EPI_TB; j++) acc[j] = 0.0f;
-  for (uint32_t sp = 0; sp < S; sp++) {
-    const float* src = part + ((size_t)sp * mpad + m0) * ld + nB + c;
+  for (uint32_t sp = 0; sp < u.S; sp++) {
+    const float* src = u.sk_part + (((size_t)sp * tail + t) * u.BT + r0) * 128u + c;
     float v[U_EPI_TB];
 #pragma unroll
-    for (int j = 0; j < U_EPI_TB; j++) v[j] = __ldcg(src + (size_t)j * ld);      // rows up to the slab's padding exist
+    for (int j = 0; j < U_EPI_TB; j++) v[j] = __ldcg(src + (size_t)j * 128u);      // rows up to the tile's padding exist
 #pragma unroll
     for (int j = 0; j < U_EPI_TB; j++) acc[j] += v[j];
   }
-  epilogue_cols<U_EPI_TB>(p, m0, nB, c, acc, sh, 1, epilogue_vec_ok(p), 0u);
+  epilogue_cols<U_EPI_TB>(p, m0, nt * 128u, c, acc, sh, 1, epilogue_vec_ok(p), 0u);
 }
 
 // ---- fused-norm prologue as one pass: X fp32 [M][ldx] -> X' fp16 [M][K] (src/ops/gemm.js:63-67)
@@ -526,19 +543,32 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // ---- split-K: when the tiles leave SMs idle (few output columns) or the last round is nearly empty, each tile's k loop
   // is cut into S units whose fp32 partial sums a second kernel adds.  Never for conv3 (S would depend on M, and chunked
   // and whole-clip calls must add in the same order).
-  u.S = 1u; u.ks_per = KSn;
+  const uint32_t tiles_all = u.n_tiles * u.m_tiles;
+  u.S = 1u; u.ks_per = KSn; u.T0 = tiles_all;
   if (p.xmode != P0P_X_CONV3) {
-    const uint64_t tiles = (uint64_t)u.n_tiles * u.m_tiles;
+    const uint64_t tiles = tiles_all;
     const uint64_t kstep = std::max<uint64_t>(5u * BT / 2u, 750u), epi = 24u * BT;
-    uint64_t best = ((tiles + sms - 1) / sms) * (KSn * kstep + (u.NACC == 1u ? epi : 0u));
+    const uint64_t whole = KSn * kstep + (u.NACC == 1u ? epi : 0u);                  // one unsplit tile
+    uint64_t best = ((tiles + sms - 1) / sms) * whole;
+    // (a) every tile split (few tiles)
     for (uint32_t S = 2u; S <= 16u; S++) {
       const uint32_t per = (KSn + S - 1u) / S;
       if (per < 8u || (uint64_t)(S - 1u) * per >= KSn) continue;                     // every unit gets k-steps, at least 8 each
       const uint64_t cost = ((tiles * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u + (uint64_t)S * BT * 40u;   // + pipeline fill per unit; second kernel: launch, partials written and read
-      if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; }
+      if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = 0u; }
+    }
+    // (b) only the tiles of the last round split over the SMs that round would leave idle
+    const uint64_t t0 = (tiles / sms) * sms, tail = tiles - t0;
+    if (t0 && tail) {
+      for (uint32_t S = 2u; S <= 16u; S++) {
+        const uint32_t per = (KSn + S - 1u) / S;
+        if (per < 4u || (uint64_t)(S - 1u) * per >= KSn) continue;
+        const uint64_t cost = (t0 / sms) * whole + ((tail * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u;
+        if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = (uint32_t)t0; }
+      }
     }
   }
-  const uint64_t sk_bytes = u.S > 1u ? (uint64_t)u.S * u.m_tiles * BT * u.n_tiles * 128u * 4u : 0u;
+  const uint64_t sk_bytes = u.S > 1u ? (uint64_t)u.S * (tiles_all - u.T0) * BT * 128u * 4u : 0u;
   if (pro_bytes + sk_bytes) {
     if (int r = ensure_scratch(c, pro_bytes + sk_bytes + 256)) return r;
   }
@@ -550,7 +580,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
     c->launches += 1;
     xbase = c->scratch;
   }
-  u.sk_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(c->scratch) + pro_bytes); u.sk_ld = u.n_tiles * 128u;
+  u.sk_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(c->scratch) + pro_bytes);
   {   // a wave of `sms` tiles reads G token tiles and sms / G weight tiles: least bytes at G = sqrt(sms * weight tile / token tile)
     const double wt = 128.0 * (p.enc == P0P_ENC_Q4 ? 0.625 : p.enc == P0P_ENC_Q8 ? 1.03125 : 2.0), xt = 2.0 * BT;
     const double g = std::sqrt((double)sms * wt / xt);
@@ -568,7 +598,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
   const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 512u);
-  const int grid = (int)std::min<uint64_t>((uint64_t)u.n_tiles * u.m_tiles * u.S, sms);
+  const int grid = (int)std::min<uint64_t>((uint64_t)u.T0 + (uint64_t)(tiles_all - u.T0) * u.S, sms);
   const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
   static bool ready = false;
@@ -588,7 +618,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");
   c->launches += 1;
   if (u.S > 1u) {
-    k_umma_finish<<<dim3(u.n_tiles, (p.M + U_EPI_TB - 1u) / U_EPI_TB), 128, 0, c->stream>>>(p, u.sk_part, u.S, u.m_tiles * BT, u.sk_ld);
+    k_umma_finish<<<dim3(tiles_all - u.T0, (BT + U_EPI_TB - 1u) / U_EPI_TB), 128, 0, c->stream>>>(u);
     if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "split-K second stage launch");
     c->launches += 1;
   }

@@ -309,6 +309,9 @@ UMMA = [
     dict(name="u split-K lnmod+heads", enc="q8", M=100, N=384, K=1536, xmode="lnmod", epi="heads", heads=dict(Ltot=128, Hq=1, Hkv=1, rowOff=7, eps=1e-6)),
     dict(name="u split-K rms+swiglu bias", enc="q4", M=40, N=512, K=2048, xmode="rms", epi="swiglu", bias=True),
     dict(name="u split-K f16 weights ragged K split", enc="f16", M=90, N=256, K=1600),
+    dict(name="u split-K of the last round only (149 tiles)", enc="q4", M=64, N=128 * 149, K=1024),
+    dict(name="u split-K of the last round only, rms+swiglu (150 tiles)", enc="q8", M=100, N=2 * 64 * 150, K=512, xmode="rms", epi="swiglu"),
+    dict(name="u split-K of the last round only, wide tiles resadd (2 x 75 tiles)", enc="q4", M=600, N=128 * 75, K=768, epi="resadd"),
     dict(name="u q4 M384 one wide tile, ring wrap", enc="q4", M=384, N=640, K=1280),
     dict(name="u q8 M777 wide tiles, many", enc="q8", M=777, N=2560, K=448, epi="resadd"),
     dict(name="u q4 M250 single accumulator, narrow", enc="q4", M=250, N=1280, K=192, epi="swiglu"),
