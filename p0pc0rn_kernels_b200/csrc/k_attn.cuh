@@ -19,17 +19,21 @@ struct AttnP {
 };
 
 constexpr int AT_BQ = 64, AT_BK = 64, AT_LD = 136;                       // 136 halves per row: fragment loads and ldmatrix rows hit distinct banks
-constexpr int AT_SMEM = 3 * AT_BQ * AT_LD * 2;
+constexpr int AT_TILE = AT_BK * AT_LD;                                   // halves of one K or V tile
+constexpr int AT_SMEM = (AT_BQ * AT_LD + 4 * AT_TILE) * 2;               // Q + two stages of (K, V)
 
 __device__ __forceinline__ void at_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void at_cp16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void at_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void at_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) { __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&h); }
 
 __global__ void __launch_bounds__(128) k_attn128(const AttnP p) {
   extern __shared__ __align__(16) unsigned char at_smem[];
-  __half* Qs = reinterpret_cast<__half*>(at_smem); __half* Ks = Qs + AT_BQ * AT_LD; __half* Vs = Ks + AT_BK * AT_LD;
+  __half* Qs = reinterpret_cast<__half*>(at_smem); __half* KV = Qs + AT_BQ * AT_LD;            // KV: [stage][K | V][64][AT_LD]
   const uint32_t tid = threadIdx.x, w = tid >> 5, lane = tid & 31u, g = lane >> 2, t4 = lane & 3u;
   const uint32_t h = blockIdx.y, hk = h / (p.Hq / p.Hkv), q0 = blockIdx.x * AT_BQ;
   const __half* Qg = p.Q + (size_t)h * p.Lq * 128u; const __half* Kg = p.K + (size_t)hk * p.Lk * 128u; const __half* Vg = p.V + (size_t)hk * p.Lk * 128u;
@@ -54,23 +58,37 @@ __global__ void __launch_bounds__(128) k_attn128(const AttnP p) {
   for (int d = 0; d < 16; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.0f, 0.0f};
   const uint32_t i0 = q0 + w * 16u + g, i1 = i0 + 8u;                                         // this thread's two query rows
-  for (uint32_t k0 = 0; k0 < kEnd; k0 += AT_BK) {
-    __syncthreads();
+  // K / V tiles arrive by cp.async, one tile ahead of the arithmetic (rows past Lk repeat the last row; they are masked)
+  auto fetch = [&](uint32_t k0, uint32_t stage) {
+    const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(KV + stage * 2 * AT_TILE), vdst = kdst + AT_TILE * 2u;
     for (uint32_t i = tid; i < AT_BK * 16u; i += 128u) {
-      const uint32_t r = i >> 4, c = i & 15u, row = min(k0 + r, p.Lk - 1u);
-      *reinterpret_cast<uint4*>(Ks + r * AT_LD + c * 8u) = __ldg(reinterpret_cast<const uint4*>(Kg + (size_t)row * 128u + c * 8u));
-      *reinterpret_cast<uint4*>(Vs + r * AT_LD + c * 8u) = __ldg(reinterpret_cast<const uint4*>(Vg + (size_t)row * 128u + c * 8u));
+      const uint32_t r = i >> 4, c = i & 15u, row = min(k0 + r, p.Lk - 1u), off = (r * AT_LD + c * 8u) * 2u;
+      at_cp16(kdst + off, Kg + (size_t)row * 128u + c * 8u);
+      at_cp16(vdst + off, Vg + (size_t)row * 128u + c * 8u);
     }
+    at_cp_commit();
+  };
+  fetch(0u, 0u);
+  uint32_t stage = 0;
+  for (uint32_t k0 = 0; k0 < kEnd; k0 += AT_BK, stage ^= 1u) {
+    if (k0 + AT_BK < kEnd) { fetch(k0 + AT_BK, stage ^ 1u); at_cp_wait<1>(); } else at_cp_wait<0>();
     __syncthreads();
+    const __half* Ks = KV + stage * 2 * AT_TILE; const __half* Vs = Ks + AT_TILE;
     // ---- scores of 16 queries x 64 keys
     float s[8][4];
 #pragma unroll
-    for (int nb = 0; nb < 8; nb++) {
-      s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+    for (int nb = 0; nb < 8; nb++) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
+    // four 8 x 8 blocks of K per ldmatrix: (keys nb*8.., dims ks*16 + {0, 8, 16, 24}) = the B fragments of two 16-dim steps.
+    // The key blocks are the inner loop: consecutive multiplies go to different accumulators.
+    const uint32_t krow = (uint32_t)__cvta_generic_to_shared(Ks + (lane & 7u) * AT_LD + (lane >> 3) * 8u);
 #pragma unroll
-      for (int ks = 0; ks < 8; ks++) {
-        const __half* b = Ks + (nb * 8 + g) * AT_LD + ks * 16 + 2u * t4;
-        at_mma(s[nb], qa[ks], *reinterpret_cast<const uint32_t*>(b), *reinterpret_cast<const uint32_t*>(b + 8));
+    for (int ks = 0; ks < 8; ks += 2) {
+#pragma unroll
+      for (int nb = 0; nb < 8; nb++) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(krow + (uint32_t)(nb * 8 * AT_LD * 2 + ks * 32)));
+        at_mma(s[nb], qa[ks], b0, b1);
+        at_mma(s[nb], qa[ks + 1], b2, b3);
       }
     }
     // ---- scale, mask, running maximum
@@ -113,6 +131,7 @@ __global__ void __launch_bounds__(128) k_attn128(const AttnP p) {
         at_mma(o[d], pa, b0, b1);
       }
     }
+    __syncthreads();                 // everyone is done with this stage before the fetch of the tile after next overwrites it
   }
   // ---- normalise and store (token-major, head h at column h * 128)
 #pragma unroll
