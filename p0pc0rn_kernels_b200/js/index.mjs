@@ -77,6 +77,7 @@ export function gemm(gpu, a) {
     x: a.x.buf.handle, w: a.w.buf.handle, y: a.y.buf.handle, st: a.stats && a.stats.buf.handle, pv: a.pv && a.pv.buf.handle, ev: a.ev && a.ev.buf.handle,
     bv: a.bv && a.bv.buf.handle, rp: h.rope && h.rope.buf.handle, gt: a.gt && a.gt.buf.handle,
     x_off: a.x.off || 0, w_off: a.w.off || 0, y_off: a.y.off || 0, w_bytes: a.w.bytes || 0, x_size: a.x.size || 0, y_size: a.y.size || 0,
+    y_peers: a.y.peers ? a.y.peers.map((b) => b.handle) : undefined,   // multi-GPU extension: other ranks' copies of y (not in the reference)
   };
   return gpu._call(() => addon.gemm(gpu._h, flat));
 }
