@@ -20,7 +20,7 @@ struct AttnP {
 
 constexpr int AT_BQ = 64, AT_BK = 64, AT_LD = 136;                       // 136 halves per row: fragment loads and ldmatrix rows hit distinct banks
 constexpr int AT_TILE = AT_BK * AT_LD;                                   // halves of one K or V tile
-constexpr int AT_SMEM = (AT_BQ * AT_LD + 4 * AT_TILE) * 2;               // Q + two stages of (K, V)
+constexpr int AT_SMEM = 4 * AT_TILE * 2;                                 // two stages of (K, V); the Q tile borrows the first before the key loop
 
 __device__ __forceinline__ void at_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -33,7 +33,7 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) { __half2 h = __
 
 __global__ void __launch_bounds__(128) k_attn128(const AttnP p) {
   extern __shared__ __align__(16) unsigned char at_smem[];
-  __half* Qs = reinterpret_cast<__half*>(at_smem); __half* KV = Qs + AT_BQ * AT_LD;            // KV: [stage][K | V][64][AT_LD]
+  __half* Qs = reinterpret_cast<__half*>(at_smem); __half* KV = Qs;                            // KV: [stage][K | V][64][AT_LD]; Q lives there until its fragments are in registers
   const uint32_t tid = threadIdx.x, w = tid >> 5, lane = tid & 31u, g = lane >> 2, t4 = lane & 3u;
   const uint32_t h = blockIdx.y, hk = h / (p.Hq / p.Hkv), q0 = blockIdx.x * AT_BQ;
   const __half* Qg = p.Q + (size_t)h * p.Lq * 128u; const __half* Kg = p.K + (size_t)hk * p.Lk * 128u; const __half* Vg = p.V + (size_t)hk * p.Lk * 128u;
@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(128) k_attn128(const AttnP p) {
     }
     at_cp_commit();
   };
+  __syncthreads();                   // every warp has its Q fragments: the tile's space is free
   fetch(0u, 0u);
   uint32_t stage = 0;
   for (uint32_t k0 = 0; k0 < kEnd; k0 += AT_BK, stage ^= 1u) {
