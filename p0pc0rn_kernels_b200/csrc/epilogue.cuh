@@ -97,6 +97,16 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     const bool half_mode = epi == P0P_EPI_HEADS && (p.flags & P0P_F_ROPE_HALF);
     const uint32_t hd = nB / 128u, sec = epi == P0P_EPI_ONORMGATE ? 0u : (hd < p.Hq ? 0u : hd < p.Hq + p.Hkv ? 1u : 2u);
     float v[TB];
+    // the rotation table is fetched first: its L2 latency then hides behind the norm's reduction instead of following it
+    float cs[TB], sn[TB];
+    if (epi == P0P_EPI_HEADS && sec < 2u) {
+      const uint32_t ang = half_mode ? (c & 63u) : (c >> 1);
+#pragma unroll
+      for (int j = 0; j < TB; j++) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(p.RP + ((size_t)p.rowOff + min(m0 + j, p.M - 1u)) * 128u) + ang);
+        cs[j] = t.x; sn[j] = t.y;
+      }
+    }
     if (sec < 2u) {                   // Q, K (and onormgate): RMS norm over the block's 128 columns; V heads pass through
       // ---- sum of squares over the 128 columns, per token
       if (TB == 16) {
@@ -161,13 +171,7 @@ __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t
     // the section and rotation mode are uniform over the block: chosen outside the token loops, which stay branch-free
     // (all of a pass's cos / sin loads in flight together)
     if (sec < 2u) {
-      float cs[TB], sn[TB], other[TB];
-      const uint32_t ang = half_mode ? (c & 63u) : (c >> 1);
-#pragma unroll
-      for (int j = 0; j < TB; j++) {
-        const float2 t = __ldg(reinterpret_cast<const float2*>(p.RP + ((size_t)p.rowOff + min(m0 + j, p.M - 1u)) * 128u) + ang);
-        cs[j] = t.x; sn[j] = t.y;
-      }
+      float other[TB];
       if (half_mode) {            // pairs (d, d+64), angle index d & 63
 #pragma unroll
         for (int j = 0; j < TB; j++) xch[j * 128 + c] = v[j];
