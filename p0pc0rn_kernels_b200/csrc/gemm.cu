@@ -159,8 +159,12 @@ extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a_in, double* flops) {
   int rc = 0;
   // The streaming kernel wins up to 8 tokens (it never dequantises); from 9 on its second token group doubles its work and
   // the tensor-core kernel (narrow tiles, K-split accumulators, split-K) is faster on every shape measured.
+  // (5 to 8 tokens over a small weight, under 16 MB: the stream is too short to pay for the two launches and the split-K
+  // reduction; measured 14.7 against 19.3 us at 4096 x 4096.)
   const bool dec_ok = decode_supported(p), um_ok = umma_supported(c, p);
-  if (want == P0P_K_DECODE || (want == P0P_K_AUTO && dec_ok && (p.M <= 8u || !um_ok))) {
+  const uint64_t stream_bytes = (uint64_t)N * K * (a->enc == P0P_ENC_Q4 ? 5u : 8u) / 8u;
+  const bool small_weight = p.M >= 5u && stream_bytes <= (16ull << 20);
+  if (want == P0P_K_DECODE || (want == P0P_K_AUTO && dec_ok && ((p.M <= 8u && !small_weight) || !um_ok))) {
     if (!dec_ok) return fail(c, -9, "gemm: the decode kernel does not take this configuration");
     rc = launch_decode(c, p); used = P0P_K_DECODE;
   } else if (want == P0P_K_UMMA || (want == P0P_K_AUTO && um_ok)) {

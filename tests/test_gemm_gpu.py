@@ -405,11 +405,12 @@ def test_decode_kernel(gpu, oracle, case):
     CS.check(got, CS.run_oracle(h), case["name"])
     h2 = CS.build(dict(case))                                   # the library's own pick: this kernel up to 8 tokens, the tensor-core kernel from 9
     got2 = CS.run_gpu(gpu, h2)
-    if case["M"] <= 8:
+    if case["M"] <= 4:
         assert gpu.lastKernel == K_DECODE and np.array_equal(got, got2), "not deterministic run to run"
-    else:
-        assert gpu.lastKernel == K_UMMA
-        CS.check(got2, CS.run_oracle(h2), case["name"] + " (library's pick)")
+    else:                                                       # 5..8 tokens: this kernel unless the weight is small; 9 and more: the tensor-core kernel
+        assert gpu.lastKernel in (K_DECODE, K_UMMA) and (case["M"] <= 8 or gpu.lastKernel == K_UMMA)
+        if gpu.lastKernel == K_DECODE: assert np.array_equal(got, got2), "not deterministic run to run"
+        else: CS.check(got2, CS.run_oracle(h2), case["name"] + " (library's pick)")
 
 
 PEERS = [
