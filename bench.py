@@ -11,13 +11,19 @@ reported as GB/s of the weight stream in `cases`.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m 512]
 
-With N > 1 (one process per GPU under torchrun) both weights are split column-wise (N) across the ranks; the
-SwiGLU output and the block output are all-gathered over NCCL.  The problem is fixed, so scaling is "strong".
-`--impl reference` times the reference's CPU path (the oracle port, all host threads) on a bounded sample.
+With N > 1 (one process per GPU under torchrun) both weights are split column-wise (N) across the ranks; every rank's
+epilogue stores its columns of the SwiGLU output and of the block output into all ranks' buffers (peer stores over
+NVLink) and the library's own flag barrier orders the ranks (NCCL all-gathers with P0P_BENCH_GATHER=nccl).  The
+problem is fixed, so scaling is "strong".  `--impl reference` times the reference's CPU path (the oracle port, all
+host threads) on the same bounded sample as the `cpu_baseline` leg.
+
+Every loop that holds a cross-rank operation runs a number of iterations that is the same on every rank by
+construction (a command-line value, or a value all-reduced first), never a per-rank clock.
 """
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -97,16 +103,24 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+_CPU_INPUTS = {}
+
+
 def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3, reps=1):
     """the reference's CPU path on a bounded sample of the block: M_rows tokens, the first gu_cols hidden columns of
-    the gate/up GEMM (RMS prologue, SwiGLU) and the first dn_cols output columns of the down GEMM (residual add)"""
+    the gate/up GEMM (RMS prologue, SwiGLU) and the first dn_cols output columns of the down GEMM (residual add).
+    Returns (flops, seconds) of `reps` passes; the inputs of a sample size are generated once and reused."""
     import oracle as O
-    rs = np.random.default_rng(seed)
-    X = O.round_f16(rs.standard_normal(M_rows * HID).astype(np.float32))
-    gamma = (1 + 0.1 * rs.standard_normal(HID)).astype(np.float32)
-    Wgu, _ = O.pack_q4((rs.standard_normal(2 * gu_cols * HID) * 0.02).astype(np.float32), 2 * gu_cols, HID)
-    Wdn, _ = O.pack_q4((rs.standard_normal(dn_cols * FF) * 0.02).astype(np.float32), dn_cols, FF)
-    Hfull = O.to_f16(rs.standard_normal(M_rows * FF).astype(np.float32))
+    key = (M_rows, gu_cols, dn_cols, seed)
+    if key not in _CPU_INPUTS:
+        rs = np.random.default_rng(seed)
+        X = O.round_f16(rs.standard_normal(M_rows * HID).astype(np.float32))
+        gamma = (1 + 0.1 * rs.standard_normal(HID)).astype(np.float32)
+        Wgu, _ = O.pack_q4((rs.standard_normal(2 * gu_cols * HID) * 0.02).astype(np.float32), 2 * gu_cols, HID)
+        Wdn, _ = O.pack_q4((rs.standard_normal(dn_cols * FF) * 0.02).astype(np.float32), dn_cols, FF)
+        Hfull = O.to_f16(rs.standard_normal(M_rows * FF).astype(np.float32))
+        _CPU_INPUTS[key] = (X, gamma, Wgu, Wdn, Hfull)
+    X, gamma, Wgu, Wdn, Hfull = _CPU_INPUTS[key]
     t0 = time.perf_counter()
     for _ in range(reps):
         ST = O.rowstats(X, M_rows, HID, rms=True)
@@ -120,26 +134,35 @@ def cpu_sample(M_rows, gu_cols, dn_cols, threads, seed=3, reps=1):
     return fl, dt
 
 
+CPU_SAMPLE = (512, FF // 2, HID // 2)      # tokens, hidden columns of gate/up, output columns of down: the bounded sample both CPU legs time
+
+
+def cpu_sample_text(rows, gu, dn):
+    return f"{rows} tokens x {gu} of {FF} hidden columns (gate/up, rms+swiglu) + {dn} of {HID} output columns (down, resadd), float64 accumulate"
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's own CPU implementation of the path (oracle port; the reference is JavaScript
-    and no JavaScript engine exists here), all host threads, bounded sample per step."""
+    and no JavaScript engine exists here), all host threads, the bounded sample of CPU_SAMPLE per step; the
+    single-thread rate (the reference's cpuGemm is single-threaded, test/kernels.test.js:29) beside it."""
     if rank != 0:
-        os._exit(0)
+        return
     import oracle as O
     O.build()
     thr = max(O.max_threads(), len(os.sched_getaffinity(0)))       # torchrun pins OMP_NUM_THREADS to 1: the host's cores are still there
-    rows, gu, dn = 64, 1024, 512
-    for _ in range(args.warmup): cpu_sample(1, 256, 128, thr)
+    rows, gu, dn = min(args.m, CPU_SAMPLE[0]), CPU_SAMPLE[1], CPU_SAMPLE[2]
+    for _ in range(min(args.warmup, 2)): cpu_sample(1, 256, 128, thr)
     t = 0.0; fl = 0.0
     for _ in range(args.steps):
         f, d = cpu_sample(rows, gu, dn, thr); fl += f; t += d
     v = fl / t / 1e12
-    sample = f"{rows} tokens x {gu} of {FF} hidden columns (gate/up, rms+swiglu) + {dn} of {HID} output columns (down, resadd), float64 accumulate"
+    f1, d1 = cpu_sample(128, 1024, 512, 1)
+    sample = cpu_sample_text(rows, gu, dn)
     print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": t / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate of f16 products",
                       "data": "synthetic", "config": {"workload": f"LLM MLP block q4, M={args.m} (configs[1]); CPU sample per step: {sample}"},
-                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": thr, "kind": "port", "sample": sample},
-                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": thr, "kind": "port", "sample": sample, "single_thread_value": f1 / d1 / 1e12},
+                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)
 
 
 def run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world):
@@ -189,7 +212,6 @@ def run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world):
         gpu.drainPool()
     torch.cuda.synchronize()
     sys.stdout.flush()
-    os._exit(0)
 
 
 def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
@@ -297,7 +319,14 @@ def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
                               "frac_tensor_whole": fl / (ms_w * 1e-3) / 1e12 / pk["tensor"], "chunks_bit_identical_to_whole": same}), flush=True)
     torch.cuda.synchronize()
     sys.stdout.flush()
-    os._exit(0)
+
+
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
+# command, see profiles/), keyed by (call, tokens, kernel family, ranks, kernel plan).  A launch whose plan differs from the
+# captured one reports null rather than a stale figure.
+TRAFFIC = {
+    ("gate_up", 512, "umma", 1): {"bytes": 82290944.0, "plan": "448 tiles of 128 x 256, last round split along K", "captured_at": "6a3c1fe"},
+}
 
 
 def main():
@@ -308,6 +337,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=512, help="tokens per step of the headline (512 = the tensor-bound case of the config)")
     ap.add_argument("--copies", type=int, default=3, help="weight copies rotated through so that every step streams from HBM")
+    ap.add_argument("--rounds", type=int, default=5, help="the headline is the median of this many rounds of --steps steps")
     ap.add_argument("--skip-cases", action="store_true", help="only the headline (for profiler captures)")
     ap.add_argument("--kernel", default=None, help="force a kernel family (generic | decode | umma)")
     ap.add_argument("--shape", default=None, help="enc:M:N:K[,enc:M:N:K...]  time plain GEMMs of these shapes instead of the block (q4|q8|f16)")
@@ -324,7 +354,8 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a short time-out: should the ranks ever disagree on a collective, the run ends with an error instead of spinning
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     # every launch of the library and every torch op / event below shares ONE non-default stream
@@ -333,11 +364,22 @@ def main():
     gpu = P.createGpu({"device": local, "stream": stream.cuda_stream})
     pk = peaks()
 
-    if args.shape or args.sweep:
-        return run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world)
-    if args.config:
-        return run_configs(args, P, torch, gpu, stream, dev, pk, rank, world)
+    try:
+        if args.shape or args.sweep:
+            run_shapes(args, P, torch, gpu, stream, dev, pk, rank, world)
+        elif args.config:
+            run_configs(args, P, torch, gpu, stream, dev, pk, rank, world)
+        else:
+            run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local)
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush(); sys.stderr.flush()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
 
+
+def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
     # ---- model state: this rank's column shard of both weights (the whole weights at N = 1), `copies` times
     ffl, hidl = FF // world, HID // world
     gu_full = synth_q4(2 * FF, HID, 1, P); dn_full = synth_q4(HID, FF, 2, P)
@@ -364,25 +406,40 @@ def main():
     hl_t = torch.zeros(Mmax * ffl, dtype=torch.float16, device=dev); hl = wrap(hl_t)                # this rank's SwiGLU columns (gather path)
     if world == 1: hf, hf_t = hl, hl_t
     else: hf = gpu.buffer(Mmax * FF * 2, "hidden", shareable=True); hf_t = torch.as_tensor(DevView(hf, Mmax * FF, "<f2"), device=dev)   # the full hidden row
-    # ---- N > 1: every rank maps the others' hidden and residual buffers; the epilogues then store each rank's columns into all
-    # copies (peer stores over NVLink) and a one-element all-reduce orders the ranks, instead of an all-gather plus re-layout
-    hf_peers, x_peers, fused = [], [], False
+    # ---- N > 1: every rank maps the others' hidden and residual buffers and flag blocks; the epilogues then store each rank's
+    # columns into all copies (peer stores over NVLink) and the library's flag barrier orders the ranks, instead of an all-gather
+    # plus re-layout.  Every rank runs the same collectives here whatever fails locally: a failure travels as data.
+    hf_peers, x_peers, flag_peers, flags, fused = [], [], [None] * world, None, False
     if world > 1 and os.environ.get("P0P_BENCH_GATHER", "") != "nccl":
+        mine, err = None, None
         try:
-            mine = (gpu.ipcExport(hf), gpu.ipcExport(xb)); every = [None] * world
-            dist.all_gather_object(every, mine)
-            for r, (hh, hx) in enumerate(every):
-                if r != rank:
-                    hf_peers.append(gpu.ipcOpen(hh, Mmax * FF * 2, f"hidden@{r}")); x_peers.append(gpu.ipcOpen(hx, Mmax * HID * 4, f"residual@{r}"))
-            fused = True
-        except Exception as e:                                                   # no peer access on this box: the NCCL gather path below
-            if rank == 0: print(f"peer mapping failed ({e}); using NCCL all-gathers", file=sys.stderr)
-            hf_peers, x_peers, fused = [], [], False
+            flags = gpu.buffer(gpu.PEER_FLAG_BYTES, "flags", shareable=True)
+            mine = (gpu.ipcExport(hf), gpu.ipcExport(xb), gpu.ipcExport(flags))
+        except Exception as e:
+            err = str(e)
+        every = [None] * world
+        dist.all_gather_object(every, mine)
+        if all(h is not None for h in every):
+            try:
+                for r, (hh, hx, hfl) in enumerate(every):
+                    if r != rank:
+                        hf_peers.append(gpu.ipcOpen(hh, Mmax * FF * 2, f"hidden@{r}")); x_peers.append(gpu.ipcOpen(hx, Mmax * HID * 4, f"residual@{r}"))
+                        flag_peers[r] = gpu.ipcOpen(hfl, gpu.PEER_FLAG_BYTES, f"flags@{r}")
+                fused = True
+            except Exception as e:                                               # no peer access on this box: the NCCL gather path below
+                err = str(e)
         ok_t = torch.tensor([1 if fused else 0], device=dev); dist.all_reduce(ok_t, op=dist.ReduceOp.MIN); fused = bool(ok_t.item())
-    flag_t = torch.zeros(1, dtype=torch.float32, device=dev)
+        if not fused:
+            if rank == 0: print(f"peer mapping failed ({err}); using NCCL all-gathers", file=sys.stderr)
+            hf_peers, x_peers = [], []
+    BARRIER_CYCLES = 10_000_000_000          # bounded wait of the flag barrier: seconds, far above any skew between ranks in lockstep
     x_host = np.random.default_rng(5).standard_normal(Mmax * HID).astype(np.float32)
     x_t.copy_(torch.from_numpy(x_host))
     launches = {"n": 0}
+
+    def order_ranks():
+        """every rank's columns are in every copy once all ranks are past this point of their streams"""
+        if fused: gpu.peerBarrier(flags, flag_peers, rank, world, BARRIER_CYCLES)
 
     def block(M, i, gather=True):
         """one pass of the MLP block over M tokens with weight copy i"""
@@ -392,7 +449,7 @@ def main():
              "y": yh, "M": M, "N": 2 * ffl, "K": HID, "wr0": 0, "wr1": ffl, "epi": "swiglu", "stats": {"buf": st}, "pv": {"buf": gamma}}
         if args.kernel: a["kernel"] = args.kernel
         P.gemm(gpu, a)
-        if fused and gather: dist.all_reduce(flag_t)                                # every rank's columns are in every copy once all ranks are here
+        if fused and gather: order_ranks()
         elif world > 1 and gather:
             hf_t[: M * FF].view(M, FF).copy_(P.all_gather_columns(hl_t[: M * ffl].view(M, ffl)))
         # residual add, in place, into this rank's columns of the (replicated) fp32 residual stream
@@ -400,7 +457,7 @@ def main():
              "y": {"buf": xb, "ld": HID, "n0": rank * hidl, "peers": x_peers if fused else []}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
         if args.kernel: a["kernel"] = args.kernel
         P.gemm(gpu, a)
-        if fused and gather: dist.all_reduce(flag_t)
+        if fused and gather: order_ranks()
         elif world > 1 and gather:
             xv = x_t[: M * HID].view(M, HID)
             xv.copy_(P.all_gather_columns(xv[:, rank * hidl:(rank + 1) * hidl]))
@@ -417,13 +474,8 @@ def main():
             gs.append(g)
         return gs
 
-    def timed(M, steps, warmup, gather=True):
-        """exactly `steps` steps (graph replays, rotating the weight copies), device time, max over ranks"""
-        l0 = gpu.launches
-        block(M, 0, gather)
-        per_step = gpu.launches - l0
-        gs = graphs_of(lambda i: block(M, i, gather))
-        for s in range(warmup): gs[s % args.copies].replay()
+    def run_steps(gs, steps):
+        """exactly `steps` graph replays bracketed by barrier + synchronize on both sides; device time, max over ranks"""
         torch.cuda.synchronize()
         if world > 1: dist.barrier()
         torch.cuda.synchronize()
@@ -434,10 +486,20 @@ def main():
         torch.cuda.synchronize()
         if world > 1: dist.barrier()
         ms = e0.elapsed_time(e1)
-        launches["n"] = per_step * steps
         if world > 1:
             t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
         return ms / steps
+
+    def timed(M, steps, warmup, rounds, gather=True):
+        """median over `rounds` rounds of exactly `steps` steps each (the weight copies rotate through every round)"""
+        l0 = gpu.launches
+        block(M, 0, gather)
+        per_step = gpu.launches - l0
+        gs = graphs_of(lambda i: block(M, i, gather))
+        for s in range(warmup): gs[s % args.copies].replay()
+        per_round = [run_steps(gs, steps) for _ in range(rounds)]
+        launches["n"] = per_step * steps
+        return float(np.median(per_round)), per_round, gs
 
     def one_gemm(M, which, i):
         if which == "gate_up":
@@ -450,8 +512,8 @@ def main():
         P.gemm(gpu, a)
 
     def kernel_ms(M, which, reps):
-        """average device time of ONE gemm call of the block (gate/up or down): graphs of that call alone, replayed
-        back to back over the rotating weight copies, CUDA events around the run"""
+        """average device time of ONE gemm call of the block (gate/up or down): graphs of that call alone (no cross-rank
+        operation inside), replayed back to back over the rotating weight copies, CUDA events around the run"""
         P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
         gs = graphs_of(lambda i: one_gemm(M, which, i))
         fam = gpu.lastKernel
@@ -464,19 +526,18 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps, fam
 
-    # ---- headline: K timed steps at M = args.m
+    # ---- headline: the median of `rounds` rounds of K timed steps at M = args.m
     M = args.m
-    sampler = ClockSampler(local);
+    sampler = ClockSampler(local)
     if rank == 0: sampler.start()
-    ms = timed(M, args.steps, max(3, args.warmup))
+    ms, per_round, gs_head = timed(M, args.steps, max(3, args.warmup), max(1, args.rounds))
     n_launch = launches["n"]
     gu_ms, gu_kernel = kernel_ms(M, "gate_up", max(20, min(100, args.steps)))
-    # keep the GPU under the same load until the sampler (200 ms period) has a few readings of the clocks
-    t_end = time.time() + 1.2
-    gs_load = graphs_of(lambda i: block(M, i, True))
-    while time.time() < t_end:
-        for s in range(50): gs_load[s % args.copies].replay()
-        torch.cuda.synchronize()
+    # keep the GPU under the same load until the sampler (200 ms period) has a few readings of the clocks.  The replay count
+    # comes from `ms`, which was all-reduced above: the same on every rank (each replay holds cross-rank barriers).
+    n_load = int(min(20000, max(50, 1.2 / (ms * 1e-3))))
+    for s in range(n_load): gs_head[s % args.copies].replay()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     value = block_flops(M) / (ms * 1e-3) / 1e12
 
@@ -507,15 +568,18 @@ def main():
     h2d = M * HID * 4
     e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms}
 
-    # ---- N > 1: one more block from the same tokens, checked.  Every rank's copy of the residual must hold the same bits (each
-    # rank wrote its columns into all copies), and rank 0 compares it with the same block run unsharded on its own GPU.
+    # ---- N > 1: one more block from the same tokens, checked.  Every rank's copy of the hidden row and of the residual must
+    # hold the same bits (each rank wrote its columns into all copies): element-wise MAX and MIN over the ranks agree.  Rank 0
+    # also compares the residual with the same block run unsharded on its own GPU.  A failed check ends the run non-zero.
     check = None
     if world > 1:
         x_t[: M * HID].copy_(torch.from_numpy(x_host[: M * HID])); torch.cuda.synchronize(); dist.barrier()
         block(M, 0); torch.cuda.synchronize(); dist.barrier()
-        mine_sum = x_t[: M * HID].view(torch.int32).to(torch.int64).sum().reshape(1)
-        sums = [torch.zeros_like(mine_sum) for _ in range(world)]; dist.all_gather(sums, mine_sum)
-        identical = all(int(v.item()) == int(sums[0].item()) for v in sums)
+        identical = {}
+        for name, tns in (("hidden", hf_t[: M * FF].view(torch.int16).to(torch.int32)), ("residual", x_t[: M * HID].view(torch.int32).clone())):
+            hi, lo = tns.clone(), tns.clone()
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX); dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            identical[name] = bool(torch.equal(hi, lo))
         rel = None
         if rank == 0:
             got = x_t[: M * HID].clone()
@@ -530,15 +594,18 @@ def main():
             rel = float(((got - x2_t).double().norm() / x2_t.double().norm()).item())
             for bfr in (Wg, Wd, x2, h2): gpu.free(bfr)
         dist.barrier()
-        check = {"replicas_bit_identical": identical, "rel_l2_vs_unsharded_on_rank0": rel}
-        if rank == 0 and (not identical or rel is None or rel > 1e-3):
-            print(f"MULTI-GPU CHECK FAILED: {check}", file=sys.stderr)
+        check = {"replicas_bit_identical": identical["residual"], "hidden_replicas_bit_identical": identical["hidden"], "rel_l2_vs_unsharded_on_rank0": rel}
+        bad = torch.tensor([0 if (identical["residual"] and identical["hidden"] and (rank != 0 or (rel is not None and rel <= 1e-3))) else 1], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            if rank == 0: print(f"MULTI-GPU CHECK FAILED: {check}", file=sys.stderr)
+            raise SystemExit(3)
 
     # ---- decode-sized cases of the same config (HBM-bound): GB/s of the algorithmic bytes
     cases = []
     if not args.skip_cases:
         for Mc in (1, 16):
-            msc = timed(Mc, max(20, args.steps), 5, gather=True)
+            msc, _, _ = timed(Mc, max(20, args.steps), 5, 3, gather=True)
             gbs = block_bytes(Mc) / world / (msc * 1e-3) / 1e9 if world > 1 else block_bytes(Mc) / (msc * 1e-3) / 1e9
             kms, kk = kernel_ms(Mc, "gate_up", 60)
             dms, _ = kernel_ms(Mc, "down", 60)
@@ -550,44 +617,38 @@ def main():
 
     # ---- roofline of the dominant kernel (gate/up GEMM: 2/3 of the block's FLOPs)
     gu_flops = 2.0 * M * (2 * ffl) * HID
-    traffic = None
-    tp = os.path.join(ROOT, "profiles", "traffic.txt")           # "<key> <dram bytes per launch>" lines taken from the ncu captures
-    if os.path.exists(tp):
-        for line in open(tp):
-            f = line.split()
-            if len(f) >= 2 and f[0] == f"gate_up_M{M}_{P._lib.KERNEL_NAMES.get(gu_kernel)}_x{world}":
-                traffic = float(f[1])
-    roof = {"bound": "tensor", "achieved": gu_flops / (gu_ms * 1e-3) / 1e12, "peak": pk["tensor"], "unit": "TFLOP/s", "traffic": traffic,
-            "kernel": f"gate/up GEMM call ({P._lib.KERNEL_NAMES.get(gu_kernel)} family: norm pre-pass + tensor-core kernel), M={M}", "ms_per_launch": gu_ms, "peak_source": pk["src"] + " (burst cuBLAS bf16)"}
+    fam_name = P._lib.KERNEL_NAMES.get(gu_kernel)
+    tr = TRAFFIC.get(("gate_up", M, fam_name, world))
+    roof = {"bound": "tensor", "achieved": gu_flops / (gu_ms * 1e-3) / 1e12, "peak": pk["tensor"], "unit": "TFLOP/s", "traffic": tr["bytes"] if tr else None,
+            "traffic_source": f"ncu capture at {tr['captured_at']} ({tr['plan']})" if tr else None,
+            "kernel": f"gate/up GEMM call ({fam_name} family: norm pre-pass + tensor-core kernel), M={M}", "ms_per_launch": gu_ms, "peak_source": pk["src"] + " (burst cuBLAS bf16)"}
     roof["frac"] = roof["achieved"] / roof["peak"]
 
     if rank == 0:
-        # CPU baseline: the oracle port on a bounded sample, all host threads
+        # CPU baseline: the oracle port on a bounded sample (the one --impl reference times), all host threads
         cpu = None
         if world == 1:                       # the CPU baseline is a single-GPU-run figure (and torchrun pins its ranks to one thread)
             import oracle as O
             O.build(); thr = max(O.max_threads(), len(os.sched_getaffinity(0)))
             cpu_sample(1, 256, 128, thr)
-            cm = min(M, 512)
-            f, d = cpu_sample(cm, FF // 2, HID // 2, thr, reps=4)
-            cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port",
-                   "sample": f"{cm} tokens x {FF // 2} of {FF} hidden columns (gate/up) + {HID // 2} of {HID} output columns (down), 4 passes, float64 accumulate, {d:.1f} s"}
+            rows, gu, dn = min(M, CPU_SAMPLE[0]), CPU_SAMPLE[1], CPU_SAMPLE[2]
+            f, d = cpu_sample(rows, gu, dn, thr, reps=4)
+            f1, d1 = cpu_sample(128, 1024, 512, 1)
+            cpu = {"value": f / d / 1e12, "unit": UNIT, "cores": thr, "kind": "port", "sample": cpu_sample_text(rows, gu, dn) + f", 4 passes, {d:.1f} s",
+                   "single_thread_value": f1 / d1 / 1e12}
         out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+               "rounds": len(per_round), "ms_per_step_rounds": per_round,
                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (q4 weights dequantised in-kernel)",
                "data": "synthetic",
                "config": {"workload": f"LLM MLP block q4, M={M} tokens: rowstats + gate/up K4096->2x14336 (rms, swiglu) + down K14336->4096 (resadd) (configs[1])",
-                          "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + ("" if world == 1 else " + epilogues store each rank's columns into every rank's buffers (peer stores), one-element all-reduce as barrier" if fused else " + NCCL all-gather of hidden and output"),
-                          "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)"},
+                          "hidden": HID, "ffn": FF, "tokens": M, "partition": f"N-sharded x{world}" + ("" if world == 1 else " + epilogues store each rank's columns into every rank's buffers (peer stores), flag barrier of the library's own" if fused else " + NCCL all-gather of hidden and output"),
+                          "l2": f"{args.copies} weight copies rotated ({args.copies * w_bytes / 1e6:.0f} MB per rank > 126 MB L2)",
+                          "timing": f"median of {len(per_round)} rounds of {args.steps} steps, each round bracketed by barrier + synchronize"},
                "e2e": e2e, "multi_gpu_check": check, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "cases": cases,
                "GB/s": block_bytes(M) / (ms * 1e-3) / 1e9}
         print(json.dumps(out), flush=True)
-    # leave without tearing down: CUDA graphs that hold NCCL kernels and the process group do not unwind in a safe
-    # order, and a benchmark has nothing to save
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sys.stdout.flush(); sys.stderr.flush()
-    os._exit(0)
+    del gs_head
 
 
 if __name__ == "__main__":

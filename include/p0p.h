@@ -163,6 +163,11 @@ uint64_t p0p_launch_count(const p0p_ctx* ctx);
 #define P0P_STATIC_SCRATCH_BYTES (8u << 20)
 int p0p_decode_q4_static(int device, void* stream, const void* w, const void* x, void* y, uint32_t M, uint32_t N, uint32_t K,
                          char* err, size_t err_cap);
+/* No counterpart in the reference.  The kernels of p0p_decode_q4_static bound every wait they make; one that ran out leaves a
+ * code in a word next to the built-in array and the results of that call are invalid.  This reads the word after the work
+ * queued on `stream` (a 4-byte copy into a local variable plus a wait for the stream: it allocates nothing either).
+ * Returns 0, -10 when a wait ran out (`err` names the code), > 0 for a CUDA error. */
+int p0p_decode_q4_static_status(int device, void* stream, char* err, size_t err_cap);
 
 /* Peer memory (no counterpart in the reference).  p0p_alloc_shareable is p0p_alloc (zeroed, 16-byte rounded, counted) on
  * memory that other processes can map: plain cudaMalloc instead of the stream-ordered pool, never recycled.
@@ -172,6 +177,16 @@ int p0p_decode_q4_static(int device, void* stream, const void* w, const void* x,
 int p0p_alloc_shareable(p0p_ctx* ctx, uint64_t bytes, p0p_buf** out);
 int p0p_ipc_export(p0p_ctx* ctx, const p0p_buf* buf, void* handle64);
 int p0p_ipc_open(p0p_ctx* ctx, const void* handle64, uint64_t bytes, p0p_buf** out);
+/* Barrier between the ranks of one node, in stream order (no counterpart in the reference).  It is the "order the ranks"
+ * step of the y_peers scheme: queued after a p0p_gemm that stored into the peers' buffers and before the call that reads
+ * the gathered rows.  `flags` is this rank's flag block: P0P_PEER_FLAG_BYTES of zeroed memory from p0p_alloc_shareable, kept
+ * for the life of the group; peer_flags[r] (r < world, the entry at `rank` is ignored) are the other ranks' blocks opened
+ * with p0p_ipc_open.  The kernel stores this rank's barrier count into every rank's block (plain stores over NVLink) and polls
+ * its OWN block until every rank has arrived; it never loads from a peer.  Every rank must issue the same sequence of
+ * barriers.  The wait is bounded by `wait_cycles` SM clock cycles (0 = about two seconds): when it runs out, the next
+ * p0p_sync / p0p_read returns -10 and the context stays usable.  May be recorded into a graph. */
+#define P0P_PEER_FLAG_BYTES 256u
+int p0p_peer_barrier(p0p_ctx* ctx, p0p_buf* flags, p0p_buf* const* peer_flags, uint32_t rank, uint32_t world, uint64_t wait_cycles);
 
 /* attention, head_dim 128 (src/ops/attention.js:168-193; argument object types/index.d.ts `AttentionArgs`): the step after the
  * 'heads' projection.  Q [Hq][Lq][128] f16, K / V [Hkv][Lk][128] f16 head-major, O [Lq][ldo] f16 token-major at column h*128.
@@ -196,6 +211,19 @@ int p0p_dequant(p0p_ctx* ctx, uint32_t enc, const p0p_buf* w, uint64_t w_off, ui
  * The producer of the `stats` input of the fused norm prologues. */
 int p0p_rowstats(p0p_ctx* ctx, const p0p_buf* x, uint64_t x_off, uint32_t ld, uint32_t c0, uint32_t rows, uint32_t cols,
                  uint32_t mode, float eps, p0p_buf* st, uint32_t st_off);
+
+/* pixstats (src/ops/video.js:301-318): r[ro + v] = rsqrt(sum_c x[v][c]^2 / C + eps) for the V voxels of an fp16 tensor [V][C]
+ * (eps 0 = 1e-8).  The producer of `stats` for conv3's fused PixelNorm (`pn`). */
+int p0p_pixstats(p0p_ctx* ctx, const p0p_buf* x, uint64_t x_off, uint32_t V, uint32_t C, float eps, p0p_buf* r, uint32_t ro);
+/* gnPartial (src/ops/misc.js:50-73, 110-115): partial GroupNorm(32) statistics of an HWC fp16 tensor [pix][C], C a power of two
+ * 32..512: one row of 32 x (count, mean, M2, 0) per 64 pixels into rows [wgOff, wgOff + ceil(pix / 64)) of `part` (512 bytes
+ * per row, gnPartBytes).  Rows of separate calls merge, as in the reference.  *nwg (optional) = the number of rows written. */
+int p0p_gn_partial(p0p_ctx* ctx, const p0p_buf* x, uint64_t x_off, uint32_t pix, uint32_t C, p0p_buf* part, uint32_t wgOff, uint32_t* nwg);
+/* gnFinalize (src/ops/misc.js:75-104, 117-120): merges nwg partial rows (Chan's formula) and writes, at float offset ab_off of
+ * `ab`, a[C] = gamma * rstd and b[C] = beta - mean * a, so that GroupNorm(x) = a * x + b per channel: the `pv` input of conv's
+ * fused `gn`.  gamma / beta at float offsets g_off / b_off of `gb`; eps 0 = 1e-6. */
+int p0p_gn_finalize(p0p_ctx* ctx, const p0p_buf* part, uint32_t nwg, uint32_t C, float eps, const p0p_buf* gb, uint32_t g_off, uint32_t b_off,
+                    p0p_buf* ab, uint32_t ab_off);
 
 /* ---- host-side helpers (no device work) ------------------------------------------------------------------ */
 uint16_t p0p_f2h(float v);                                   /* f2h  (src/core/gpu.js:276-291) */

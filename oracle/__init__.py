@@ -160,6 +160,24 @@ def rowstats(X, rows: int, cols: int, ld: int | None = None, rms: bool = False, 
     lib().orc_rowstats(_p(X), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(ld or cols), C.c_int(1 if rms else 0), C.c_float(eps), _p(ST)); return ST
 
 
+def pixstats(X16, V: int, Cc: int, eps: float = 1e-8) -> np.ndarray:
+    """pixstats of src/ops/video.js:301-318 on fp16 bits [V][C] -> float32 [V]"""
+    X16 = np.ascontiguousarray(X16, np.uint16).ravel(); R = np.empty(V, np.float32)
+    lib().orc_pixstats(_p(X16), C.c_uint32(V), C.c_uint32(Cc), C.c_float(eps), _p(R)); return R
+
+
+def gn_partial(X16, pix: int, Cc: int) -> np.ndarray:
+    """gnPartial of src/ops/misc.js:50-73 -> float32 [ceil(pix/64)][32][4] = (n, mean, M2, 0)"""
+    X16 = np.ascontiguousarray(X16, np.uint16).ravel(); nwg = -(-pix // 64); PT = np.zeros(nwg * 32 * 4, np.float32)
+    lib().orc_gn_partial(_p(X16), C.c_uint32(pix), C.c_uint32(Cc), C.c_uint32(0), _p(PT)); return PT
+
+
+def gn_finalize(PT, nwg: int, Cc: int, gamma, beta, eps: float = 1e-6) -> np.ndarray:
+    """gnFinalize of src/ops/misc.js:75-104 -> float32 [2][C] = a, b"""
+    PT = _f32(PT).ravel(); gamma = _f32(gamma).ravel(); beta = _f32(beta).ravel(); AB = np.empty(2 * Cc, np.float32)
+    lib().orc_gn_finalize(_p(PT), C.c_uint32(nwg), C.c_uint32(Cc), C.c_float(eps), _p(gamma), _p(beta), _p(AB)); return AB
+
+
 def cpu_attn(Q, Kt, V, *, Hq: int, Hkv: int | None = None, Lq: int, Lk: int | None = None, D: int = 128, mode: int = 0, nvalid: int | None = None,
              scale: float | None = None, cap: float = 0.0, threads: int = 0) -> np.ndarray:
     """cpuAttn of test/kernels.test.js:32-48 -> O float32 [Lq][Hq*D]"""

@@ -505,6 +505,51 @@ API void orc_rowstats(const float* X, uint32_t rows, uint32_t cols, uint32_t ld,
   }
 }
 
+/* pixstats (src/ops/video.js:301-318): R[ro + v] = 1 / sqrt(sum_c x[v][c]^2 / C + eps), x fp16 [V][C]; the shader sums
+ * vec4 dot products in fp32, the sum is kept in float64 here and rounded once. */
+API void orc_pixstats(const uint16_t* X, uint32_t V, uint32_t C, float eps, float* R) {
+  for (uint32_t v = 0; v < V; v++) {
+    double s = 0;
+    for (uint32_t c = 0; c < C; c++) { double x = orc_h2f(X[(size_t)v * C + c]); s += x * x; }
+    R[v] = 1.0f / sqrtf((float)(s / C) + eps);
+  }
+}
+
+/* gnPartial (src/ops/misc.js:50-73): per 64-pixel chunk and group (32 groups of C / 32 channels) the count, the mean and
+ * M2 = sum (x - mean)^2 by an exact two-pass over the chunk; PT[(wgOff + wg) * 32 + g] = (n, mean, M2, 0).  Sums in float64,
+ * the mean rounded to fp32 before the second pass as in the shader. */
+API void orc_gn_partial(const uint16_t* X, uint32_t pix, uint32_t C, uint32_t wgOff, float* PT) {
+  const uint32_t nwg = (pix + 63u) / 64u, cpg = C / 32u;
+  for (uint32_t wg = 0; wg < nwg; wg++) {
+    const uint32_t px0 = wg * 64u, npx = pix - px0 < 64u ? pix - px0 : 64u;
+    const float cnt = (float)(npx * cpg);
+    for (uint32_t g = 0; g < 32u; g++) {
+      double s = 0;
+      for (uint32_t p = 0; p < npx; p++) for (uint32_t j = 0; j < cpg; j++) s += orc_h2f(X[((size_t)px0 + p) * C + g * cpg + j]);
+      const float mean = (float)(s / (cnt > 1.0f ? cnt : 1.0f));
+      double m2 = 0;
+      for (uint32_t p = 0; p < npx; p++) for (uint32_t j = 0; j < cpg; j++) { double d = (double)(float)(orc_h2f(X[((size_t)px0 + p) * C + g * cpg + j]) - mean); m2 += d * d; }
+      float* o = PT + (((size_t)wgOff + wg) * 32u + g) * 4u;
+      o[0] = cnt; o[1] = mean; o[2] = (float)m2; o[3] = 0.0f;
+    }
+  }
+}
+
+/* gnFinalize (src/ops/misc.js:75-104): Chan's merge of the partial rows in row order (fp32, as the shader), then
+ * a[c] = gamma[c] * rstd, b[c] = beta[c] - mean * a[c]; AB = a[C] then b[C]. */
+API void orc_gn_finalize(const float* PT, uint32_t nwg, uint32_t C, float eps, const float* gamma, const float* beta, float* AB) {
+  const uint32_t cpg = C / 32u;
+  for (uint32_t g = 0; g < 32u; g++) {
+    float n = 0, mean = 0, m2 = 0;
+    for (uint32_t w = 0; w < nwg; w++) {
+      const float* q = PT + ((size_t)w * 32u + g) * 4u;
+      if (q[0] > 0.0f) { float nn = n + q[0], d = q[1] - mean; mean = mean + d * (q[0] / nn); m2 = m2 + q[2] + d * d * (n * q[0] / nn); n = nn; }
+    }
+    const float rs = 1.0f / sqrtf(m2 / (n > 1.0f ? n : 1.0f) + eps);
+    for (uint32_t c = g * cpg; c < (g + 1u) * cpg; c++) { const float a = gamma[c] * rs; AB[c] = a; AB[C + c] = beta[c] - mean * a; }
+  }
+}
+
 API int orc_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

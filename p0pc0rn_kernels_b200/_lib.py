@@ -15,8 +15,9 @@ SYMBOLS = [
     "p0p_alloc", "p0p_wrap", "p0p_free", "p0p_drain_pool", "p0p_pool_stats", "p0p_reset_peak", "p0p_buf_size", "p0p_buf_ptr",
     "p0p_write", "p0p_read", "p0p_clear", "p0p_copy", "p0p_sync", "p0p_host_alloc", "p0p_host_free",
     "p0p_capture_begin", "p0p_capture_end", "p0p_graph_launch", "p0p_graph_free",
-    "p0p_decode_q4_static", "p0p_alloc_shareable", "p0p_ipc_export", "p0p_ipc_open",
+    "p0p_decode_q4_static", "p0p_decode_q4_static_status", "p0p_alloc_shareable", "p0p_ipc_export", "p0p_ipc_open", "p0p_peer_barrier",
     "p0p_gemm", "p0p_attention", "p0p_last_kernel", "p0p_launch_count", "p0p_dequant", "p0p_rowstats",
+    "p0p_pixstats", "p0p_gn_partial", "p0p_gn_finalize",
     "p0p_f2h", "p0p_h2f", "p0p_to_f16", "p0p_from_f16", "p0p_pack_q4", "p0p_pack_q8", "p0p_reorder_conv_rows",
     "p0p_encoded_bytes", "p0p_shard_rows", "p0p_abi_version",
 ]
@@ -64,6 +65,11 @@ def _load():
         "p0p_copy": (i, [vp, vp, u64, vp, u64, u64]), "p0p_sync": (i, [vp]), "p0p_host_alloc": (i, [vp, u64, C.POINTER(vp)]), "p0p_host_free": (i, [vp, vp]),
         "p0p_capture_begin": (i, [vp]), "p0p_capture_end": (i, [vp, C.POINTER(vp)]), "p0p_graph_launch": (i, [vp, vp]), "p0p_graph_free": (i, [vp, vp]),
         "p0p_decode_q4_static": (i, [i, vp, vp, vp, vp, u32, u32, u32, C.c_char_p, C.c_size_t]),
+        "p0p_decode_q4_static_status": (i, [i, vp, C.c_char_p, C.c_size_t]),
+        "p0p_peer_barrier": (i, [vp, vp, C.POINTER(vp), u32, u32, u64]),
+        "p0p_pixstats": (i, [vp, vp, u64, u32, u32, C.c_float, vp, u32]),
+        "p0p_gn_partial": (i, [vp, vp, u64, u32, u32, vp, u32, C.POINTER(u32)]),
+        "p0p_gn_finalize": (i, [vp, vp, u32, u32, C.c_float, vp, u32, u32, vp, u32]),
         "p0p_alloc_shareable": (i, [vp, u64, C.POINTER(vp)]), "p0p_ipc_export": (i, [vp, vp, vp]), "p0p_ipc_open": (i, [vp, vp, u64, C.POINTER(vp)]),
         "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_attention": (i, [vp, C.POINTER(AttnArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]),
         "p0p_dequant": (i, [vp, u32, vp, u64, u32, u32, u32, u32, u32, vp, u64]),

@@ -1,0 +1,98 @@
+// Host side of the decode-sized multiply (k_decode.cuh): which calls it takes, the plan of a call (k-blocks, grid, shared
+// memory, split-K scratch) and the launches; and the instantiations of the stream kernel.  The second-stage kernels are
+// instantiated in decode_finish.cu.
+#include <algorithm>
+
+#include "device_once.h"
+#include "k_decode.cuh"
+
+namespace p0p {
+
+typedef void (*decode_stream_fn)(const DecodeP);
+typedef void (*decode_finish_fn)(const DecodeP);
+decode_finish_fn decode_finish_kernel(uint32_t mp, uint32_t epi);      // decode_finish.cu
+
+static decode_stream_fn stream_kernel(uint32_t enc, uint32_t xmode, uint32_t mp) {
+  // [encoding][prologue: f16, lnmod, rms][8 | 16 token columns]
+  static const decode_stream_fn table[2][3][2] = {
+      {{k_decode_stream<P0P_ENC_Q4, P0P_X_F16, 8>, k_decode_stream<P0P_ENC_Q4, P0P_X_F16, 16>},
+       {k_decode_stream<P0P_ENC_Q4, P0P_X_LNMOD, 8>, k_decode_stream<P0P_ENC_Q4, P0P_X_LNMOD, 16>},
+       {k_decode_stream<P0P_ENC_Q4, P0P_X_RMS, 8>, k_decode_stream<P0P_ENC_Q4, P0P_X_RMS, 16>}},
+      {{k_decode_stream<P0P_ENC_Q8, P0P_X_F16, 8>, k_decode_stream<P0P_ENC_Q8, P0P_X_F16, 16>},
+       {k_decode_stream<P0P_ENC_Q8, P0P_X_LNMOD, 8>, k_decode_stream<P0P_ENC_Q8, P0P_X_LNMOD, 16>},
+       {k_decode_stream<P0P_ENC_Q8, P0P_X_RMS, 8>, k_decode_stream<P0P_ENC_Q8, P0P_X_RMS, 16>}}};
+  return table[enc][xmode][mp == 8u ? 0 : 1];
+}
+
+bool decode_supported(const KP& p) {
+  if (p.M > 16u) return false;
+  if (p.enc != P0P_ENC_Q4 && p.enc != P0P_ENC_Q8) return false;
+  if (p.xmode != P0P_X_F16 && p.xmode != P0P_X_LNMOD && p.xmode != P0P_X_RMS) return false;
+  if (p.wR0 % 64u) return false;
+  if (p.epi == P0P_EPI_SWIGLU && (p.wR1 % 64u)) return false;
+  if (p.K % D_STAGE_K) return false;                  // k-blocks are whole stages
+  if ((uintptr_t)p.W & 15u) return false;             // bulk copies need 16-byte aligned sources
+  if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
+  if (p.epi == P0P_EPI_HEADS && ((uintptr_t)p.RP & 7u)) return false;      // the epilogue reads (cos, sin) as one 8-byte load
+  return true;
+}
+
+uint64_t plan_decode(DecodeP& d, DecodeLaunch& L, int sms, size_t smem_per_sm) {
+  const KP& p = d.p;
+  d.Mp = p.M <= 8u ? 8u : 16u;
+  const uint32_t cols = p.epi == P0P_EPI_SWIGLU ? p.N / 2u : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u * 128u : p.N);
+  d.th = (cols + 63u) / 64u;
+  // tiles past the weight's last row do not exist: columns there read the last tile (their outputs are never stored)
+  const uint32_t avail = (p.Nw - p.wR0) / 64u;
+  if (p.epi != P0P_EPI_SWIGLU && d.th > avail) d.th = avail;
+  d.tiles = p.epi == P0P_EPI_SWIGLU ? 2u * d.th : d.th;
+  d.nslots = d.tiles * 64u;
+  // k-block: as long as the token tile allows (about 32 KB), short enough for ~4 units per SM
+  uint32_t kc = p.M <= 8u ? 2048u : 1024u;                                // token tile of (M + 1) * kc fp16 stays near 32 KB
+  const uint64_t want_units = 4ull * (uint64_t)sms;
+  while (kc > 256u && (uint64_t)d.tiles * ((p.K + kc - 1u) / kc) < want_units) kc >>= 1;
+  if (kc > p.K) kc = p.K;
+  d.KC = kc; d.S = (p.K + kc - 1u) / kc; d.units = d.tiles * d.S;
+  const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
+  const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 16u;
+  L.smem = (size_t)D_STAGES * (p.enc == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8) + (((p.M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
+  const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, smem_per_sm / (L.smem + 1024)));
+  L.grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * (uint64_t)sms);      // every block is resident: the unit ranges run side by side
+  L.fin_blocks = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u : (((p.N + 3u) & ~3u) + 127u) / 128u;
+  return (uint64_t)d.S * p.M * d.nslots * 4ull;
+}
+
+cudaError_t launch_decode_pair(const DecodeP& d, const DecodeLaunch& L, int device, cudaStream_t st) {
+  const KP& p = d.p;
+  if (L.smem > (size_t)D_SMEM_MAX) return cudaErrorInvalidValue;
+  const decode_stream_fn stream = stream_kernel(p.enc, p.xmode, d.Mp);
+  // the dynamic shared memory ceiling is an attribute of (kernel, device): raised once for each pair
+  static DeviceOnce once[2][3][2];
+  cudaError_t e = cudaSuccess;
+  if (once[p.enc][p.xmode][d.Mp == 8u ? 0 : 1].run(device, [&] { e = cudaFuncSetAttribute(reinterpret_cast<const void*>(stream), cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_MAX); return (int)e; }))
+    return e != cudaSuccess ? e : cudaErrorInvalidDevice;
+  // both kernels are programmatic dependents of whatever precedes them in the stream (see k_decode.cuh)
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)L.grid); cfg.blockDim = dim3(D_THREADS); cfg.dynamicSmemBytes = L.smem; cfg.stream = st; cfg.attrs = at; cfg.numAttrs = 1;
+  if ((e = cudaLaunchKernelEx(&cfg, stream, d)) != cudaSuccess) return e;
+  cfg.gridDim = dim3(L.fin_blocks); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0;
+  return cudaLaunchKernelEx(&cfg, decode_finish_kernel(d.Mp, p.epi), d);
+}
+
+int launch_decode(p0p_ctx* c, const KP& p) {
+  DecodeP d{};
+  d.p = p;
+  DecodeLaunch L{};
+  const uint64_t sbytes = plan_decode(d, L, c->prop.multiProcessorCount, (size_t)c->prop.sharedMemPerMultiprocessor);
+  if (int r = ensure_scratch(c, sbytes + 256)) return r;
+  d.scratch = reinterpret_cast<float*>(c->scratch);
+  d.status = c->dev_status;
+  const cudaError_t e = launch_decode_pair(d, L, c->device, c->stream);
+  if (e != cudaSuccess) return cuda_fail(c, e, "decode launch");
+  c->launches += 2;
+  return 0;
+}
+
+}  // namespace p0p

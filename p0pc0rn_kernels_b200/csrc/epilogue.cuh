@@ -87,9 +87,11 @@ __device__ __forceinline__ void swiglu_tokens(const KP& p, uint32_t m0, uint32_t
 // nB: first column of the block (multiple of 128 for heads / onormgate).  c: this thread's column in the
 // block (0..127).  acc[j]: fp32 accumulator of (row m0 + j, column nB + c).  vec: row-wise 16-byte stores (needs
 // epilogue_vec_ok, TB == 16); par: parity of the pass (alternates between consecutive calls).
-template <int TB>
+// EPI_T: the epilogue kind as a compile-time constant (P0P_EPI_*), or -1 to read it from p.epi.  A kernel that is
+// instantiated per kind carries only that kind's code: with all seven kinds inlined a kernel grows by ~400 KB.
+template <int TB, int EPI_T = -1>
 __device__ __forceinline__ void epilogue_cols(const KP& p, uint32_t m0, uint32_t nB, uint32_t c, float (&acc)[TB], float* sh, int barid, bool vec = false, uint32_t par = 0) {
-  const uint32_t col = nB + c, epi = p.epi, lane = c & 31u, wq = c >> 5;
+  const uint32_t col = nB + c, epi = EPI_T >= 0 ? (uint32_t)EPI_T : p.epi, lane = c & 31u, wq = c >> 5;
   __half* Yh = reinterpret_cast<__half*>(p.Y); float* Yf = reinterpret_cast<float*>(p.Y);
   if (epi == P0P_EPI_HEADS || epi == P0P_EPI_ONORMGATE) {
     float* part = sh;                 // [4][TB] sums of squares per warp

@@ -8,7 +8,7 @@
 #include "k_generic.cuh"
 #include "k_aux.cuh"
 #include "k_decode.cuh"
-#include "k_umma.cuh"
+#include "umma_launch.cuh"
 
 using namespace p0p;
 

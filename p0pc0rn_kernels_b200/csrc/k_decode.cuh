@@ -15,6 +15,9 @@
 //            applied on the way in.  Each unit's 64 x M partial sums go to a scratch buffer.
 //   stage 2  k_decode_finish   sums the k-block partials in a fixed order (deterministic, no atomics) and
 //            applies the fused epilogue.
+// Both kernels are launched as programmatic dependents: stage 2 is resident before stage 1 ends, and the next call's
+// stage 1 streams its first weights while this call's stage 2 still runs; each waits (griddepcontrol.wait) before it
+// touches what the kernel before it writes.
 //
 // Every wait on an mbarrier is bounded; on a time-out the block records a code in the context's status word
 // and leaves.
@@ -241,6 +244,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   // the row of zeros that token columns past M read
   for (uint32_t i = tid; i < tok_stride / 16u; i += D_THREADS) reinterpret_cast<uint4*>(xs + (size_t)p.M * tok_stride)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
+  grid_launch_dependents();                 // the second stage may be brought onto the SMs now; it waits for this grid to finish
 
   const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * d.units) / gridDim.x), u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * d.units) / gridDim.x);
   constexpr uint32_t REC = ENC == P0P_ENC_Q4 ? 1280u : 4224u, REC_K = ENC == P0P_ENC_Q4 ? 32u : 64u;
@@ -288,6 +292,9 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   L.one = p.M == 1u;                                                     // a single token: only the accumulators of token 0 are kept up
   uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
   bool ok = true;
+  // The weights stream from the start (the producer above never waits for another kernel).  Tokens, statistics and the scratch
+  // buffer may still be in use by the kernel before this one in the stream: the consumers wait for it here.
+  grid_dependency_wait();
   // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
   // the named barriers below, so nobody is left waiting for it.
   for (uint32_t u = u0; u < u1; u++) {
@@ -349,16 +356,18 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   }
 }
 
-// ---- stage 2: fixed-order sum over the k-blocks, then the fused epilogue.  One block per 128 output columns.
-template <int MP>
+// ---- stage 2: fixed-order sum over the k-blocks, then the fused epilogue (a compile-time constant: one instantiation per
+// kind keeps this latency-bound kernel small).  One block per 128 output columns.
+template <int MP, int EPI>
 __global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
   __shared__ __align__(16) float sh[MP * 132];
   const KP& p = d.p;
   const uint32_t c = threadIdx.x, nB = blockIdx.x * 128u, col = nB + c;
   uint32_t slot;
-  if (p.epi == P0P_EPI_SWIGLU) slot = ((col & 1u) ? d.th * 64u : 0u) + (col >> 1);
+  if (EPI == P0P_EPI_SWIGLU) slot = ((col & 1u) ? d.th * 64u : 0u) + (col >> 1);
   else slot = col;
   slot = min(slot, d.nslots - 1u);
+  grid_dependency_wait();                       // the partial sums come from the stream kernel this launch may overlap with
   // the partials of one output are read in batches of eight independent loads, then added in k-block order
   float acc[MP];
 #pragma unroll
@@ -375,82 +384,17 @@ __global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
       }
     }
   }
-  epilogue_cols<MP>(p, 0u, nB, c, acc, sh, 1);
+  grid_launch_dependents();
+  epilogue_cols<MP, EPI>(p, 0u, nB, c, acc, sh, 1);
 }
 
-inline bool decode_supported(const KP& p) {
-  if (p.M > 16u) return false;
-  if (p.enc != P0P_ENC_Q4 && p.enc != P0P_ENC_Q8) return false;
-  if (p.xmode != P0P_X_F16 && p.xmode != P0P_X_LNMOD && p.xmode != P0P_X_RMS) return false;
-  if (p.wR0 % 64u) return false;
-  if (p.epi == P0P_EPI_SWIGLU && (p.wR1 % 64u)) return false;
-  if (p.K % D_STAGE_K) return false;                  // k-blocks are whole stages
-  if ((uintptr_t)p.W & 15u) return false;             // bulk copies need 16-byte aligned sources
-  if (p.enc == P0P_ENC_Q8 && (p.wk0 % 64u)) return false;
-  if (p.epi == P0P_EPI_HEADS && ((uintptr_t)p.RP & 7u)) return false;      // the epilogue reads (cos, sin) as one 8-byte load
-  return true;
-}
-
-template <int ENC, int XMODE>
-inline cudaError_t launch_decode_t(const DecodeP& d, int grid, size_t smem, cudaStream_t st) {
-  // the dynamic shared memory ceiling of each instantiation is raised once (D_SMEM_MAX covers every configuration)
-  static bool ready = false;
-  if (!ready) {
-    cudaError_t e;
-    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_MAX)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_decode_stream<ENC, XMODE, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_MAX)) != cudaSuccess) return e;
-    ready = true;
-  }
-  if (smem > (size_t)D_SMEM_MAX) return cudaErrorInvalidValue;
-  if (d.Mp == 8) k_decode_stream<ENC, XMODE, 8><<<grid, D_THREADS, smem, st>>>(d);
-  else k_decode_stream<ENC, XMODE, 16><<<grid, D_THREADS, smem, st>>>(d);
-  return cudaGetLastError();
-}
-
-inline int launch_decode(p0p_ctx* c, const KP& p) {
-  DecodeP d{};
-  d.p = p;
-  d.Mp = p.M <= 8u ? 8u : 16u;
-  const uint32_t cols = p.epi == P0P_EPI_SWIGLU ? p.N / 2u : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u * 128u : p.N);
-  d.th = (cols + 63u) / 64u;
-  // tiles past the weight's last row do not exist: columns there read the last tile (their outputs are never stored)
-  const uint32_t avail = (p.Nw - p.wR0) / 64u;
-  if (p.epi != P0P_EPI_SWIGLU && d.th > avail) d.th = avail;
-  d.tiles = p.epi == P0P_EPI_SWIGLU ? 2u * d.th : d.th;
-  d.nslots = d.tiles * 64u;
-  // k-block: as long as the token tile allows (about 32 KB), short enough for ~4 units per SM
-  const uint32_t sms = (uint32_t)c->prop.multiProcessorCount;
-  uint32_t kc = p.M <= 8u ? 2048u : 1024u;                                // token tile of (M + 1) * kc fp16 stays near 32 KB
-  const uint64_t want_units = 4ull * sms;
-  while (kc > 256u && (uint64_t)d.tiles * ((p.K + kc - 1u) / kc) < want_units) kc >>= 1;
-  if (kc > p.K) kc = p.K;
-  d.KC = kc; d.S = (p.K + kc - 1u) / kc; d.units = d.tiles * d.S;
-  const uint64_t sbytes = (uint64_t)d.S * p.M * d.nslots * 4ull;
-  if (int r = ensure_scratch(c, sbytes + 256)) return r;
-  d.scratch = reinterpret_cast<float*>(c->scratch);
-  d.status = c->dev_status;
-  const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
-  const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 16u;
-  const size_t smem = (size_t)D_STAGES * (p.enc == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8) + (((p.M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
-  const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (size_t)(c->prop.sharedMemPerMultiprocessor) / (smem + 1024)));
-  const int grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * sms);      // every block is resident: the unit ranges run side by side
-  cudaError_t e;
-  if (p.enc == P0P_ENC_Q4) {
-    if (p.xmode == P0P_X_F16) e = launch_decode_t<P0P_ENC_Q4, P0P_X_F16>(d, grid, smem, c->stream);
-    else if (p.xmode == P0P_X_RMS) e = launch_decode_t<P0P_ENC_Q4, P0P_X_RMS>(d, grid, smem, c->stream);
-    else e = launch_decode_t<P0P_ENC_Q4, P0P_X_LNMOD>(d, grid, smem, c->stream);
-  } else {
-    if (p.xmode == P0P_X_F16) e = launch_decode_t<P0P_ENC_Q8, P0P_X_F16>(d, grid, smem, c->stream);
-    else if (p.xmode == P0P_X_RMS) e = launch_decode_t<P0P_ENC_Q8, P0P_X_RMS>(d, grid, smem, c->stream);
-    else e = launch_decode_t<P0P_ENC_Q8, P0P_X_LNMOD>(d, grid, smem, c->stream);
-  }
-  if (e != cudaSuccess) return cuda_fail(c, e, "decode launch");
-  const uint32_t fin_cols = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u : (((p.N + 3u) & ~3u) + 127u) / 128u;
-  if (d.Mp == 8) k_decode_finish<8><<<fin_cols, 128, 0, c->stream>>>(d);
-  else k_decode_finish<16><<<fin_cols, 128, 0, c->stream>>>(d);
-  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(c, e, "decode finish launch");
-  c->launches += 2;
-  return 0;
-}
+// ---- host side (decode.cu): which calls the kernel pair takes, the plan of a call, the launches
+bool decode_supported(const KP& p);
+// fills tiles / k-blocks / scratch need of a call; `sms` and `smem_per_sm` describe the device.  Returns the bytes of split-K scratch.
+struct DecodeLaunch { int grid; size_t smem; uint32_t fin_blocks; };
+uint64_t plan_decode(DecodeP& d, DecodeLaunch& L, int sms, size_t smem_per_sm);
+// both kernels of a planned call on `st` (d.scratch and d.status set by the caller); device = the current device's ordinal
+cudaError_t launch_decode_pair(const DecodeP& d, const DecodeLaunch& L, int device, cudaStream_t st);
+int launch_decode(p0p_ctx* c, const KP& p);
 
 }  // namespace p0p

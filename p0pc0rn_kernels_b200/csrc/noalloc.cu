@@ -13,7 +13,10 @@
 // has to start at zero (each call overwrites exactly the words it later reads), but two calls whose kernels
 // overlap on the GPU - different streams, or graph branches - race on it: keep calls on one device in one
 // stream order.  The first call on each device looks up the array's device address (and raises one kernel
-// attribute); make that first call before any stream capture begins.
+// attribute); make that first call before any stream capture begins.  The kernels bound every wait they make; whether
+// one ran out is read back with p0p_decode_q4_static_status, which allocates nothing either.
+#include <cstdio>
+#include <cstring>
 #include <mutex>
 
 #include "k_decode.cuh"
@@ -70,13 +73,8 @@ extern "C" int p0p_decode_q4_static(int device, void* stream, const void* w, con
   p.M = M; p.N = N; p.K = K; p.ldx = K; p.wG = K / 32u; p.ldy = N; p.Nw = N; p.eps = 1e-6f; p.stride = 1; p.ks = 1;
   p.enc = P0P_ENC_Q4; p.xmode = P0P_X_F16; p.epi = P0P_EPI_F16; p.vecx = 1;
   p.X = x; p.W = reinterpret_cast<const uint8_t*>(w); p.Y = y;
-  d.Mp = M <= 8u ? 8u : 16u;
-  d.th = N / 64u; d.tiles = d.th; d.nslots = N;
-  uint32_t kc = M <= 8u ? 2048u : 1024u;
-  while (kc > 256u && (uint64_t)d.tiles * ((K + kc - 1u) / kc) < 4ull * (uint64_t)pd.sms) kc >>= 1;
-  if (kc > K) kc = K;
-  d.KC = kc; d.S = (K + kc - 1u) / kc; d.units = d.tiles * d.S;
-  const uint64_t need = (uint64_t)d.S * M * d.nslots * 4ull;
+  DecodeLaunch L{};
+  const uint64_t need = plan_decode(d, L, pd.sms, (size_t)pd.smem_per_sm);
   if (need > (uint64_t)P0P_STATIC_SCRATCH_BYTES) {
     char msg[200];
     snprintf(msg, sizeof msg, "decode_q4_static: this shape needs %llu bytes of split-K scratch, the built-in array holds %llu; use p0p_gemm",
@@ -84,19 +82,33 @@ extern "C" int p0p_decode_q4_static(int device, void* stream, const void* w, con
     return say(err, err_cap, -4, msg);
   }
   d.scratch = pd.scratch; d.status = pd.status;
-  const uint32_t tok_stride = d.KC * 2u + 64u;
-  const size_t ct_bytes = (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u;
-  const size_t smem = (size_t)D_STAGES * D_STAGE_BYTES_Q4 + (((M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
-  const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (size_t)pd.smem_per_sm / (smem + 1024)));
-  const int grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * (uint64_t)pd.sms);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(pd.status, 0, sizeof(int), st);          // the one word that must start at zero
-  if (e == cudaSuccess) e = launch_decode_t<P0P_ENC_Q4, P0P_X_F16>(d, grid, smem, st);
-  if (e == cudaSuccess) {
-    if (d.Mp == 8) k_decode_finish<8><<<N / 128u + (N % 128u ? 1u : 0u), 128, 0, st>>>(d);
-    else k_decode_finish<16><<<N / 128u + (N % 128u ? 1u : 0u), 128, 0, st>>>(d);
-    e = cudaGetLastError();
-  }
+  if (e == cudaSuccess) e = launch_decode_pair(d, L, device, st);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return say(err, err_cap, (int)e, cudaGetErrorString(e)); }
+  return 0;
+}
+
+// The kernels of p0p_decode_q4_static bound every wait; one that ran out leaves a code in a status word next to the scratch
+// array and the results of that call are invalid.  This reads the word back (a 4-byte copy into a local variable and a wait
+// for `stream`: no allocation either) after the calls queued on `stream`: 0 = fine, -10 = a wait ran out (the code is in `err`).
+extern "C" int p0p_decode_q4_static_status(int device, void* stream, char* err, size_t err_cap) {
+  using namespace p0p;
+  if (err && err_cap) err[0] = 0;
+  if (device < 0 || device >= MAX_DEVICES) return say(err, err_cap, -1, "decode_q4_static_status: device ordinal out of range");
+  DeviceGuard guard(device);
+  if (!guard.ok) return say(err, err_cap, -3, "decode_q4_static_status: cannot make the device current");
+  int* word = nullptr;
+  { std::lock_guard<std::mutex> lock(g_mu); if (g_dev[device].ready) word = g_dev[device].status; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int code = 0;
+  cudaError_t e = word ? cudaMemcpyAsync(&code, word, sizeof code, cudaMemcpyDeviceToHost, st) : cudaSuccess;
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return say(err, err_cap, (int)e, cudaGetErrorString(e)); }
+  if (code) {
+    char msg[120];
+    snprintf(msg, sizeof msg, "decode_q4_static: a kernel gave up on a bounded wait (code %d); the results of the queued calls are invalid", code);
+    return say(err, err_cap, -10, msg);
+  }
   return 0;
 }

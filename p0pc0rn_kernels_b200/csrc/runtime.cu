@@ -325,9 +325,17 @@ int p0p_graph_free(p0p_ctx* c, p0p_graph* gr) {
 }  // extern "C"
 
 namespace p0p {
+// is the context's stream recording a graph, whoever began the capture (p0p_capture_begin, or the owner of a shared stream)?
+static bool stream_is_capturing(p0p_ctx* c) {
+  if (c->capturing) return true;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(c->stream, &st) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+  return st != cudaStreamCaptureStatusNone;
+}
+
 int ensure_scratch(p0p_ctx* c, uint64_t bytes) {
   if (c->scratch_bytes >= bytes) return 0;
-  if (c->capturing) return fail(c, -11, "this call needs %llu bytes of scratch memory, which cannot be sized while recording: run it once before p0p_capture_begin", (unsigned long long)bytes);
+  if (stream_is_capturing(c)) return fail(c, -11, "this call needs %llu bytes of scratch memory, which cannot be sized while recording: run it once before p0p_capture_begin", (unsigned long long)bytes);
   if (c->scratch) { cudaStreamSynchronize(c->stream); cudaFree(c->scratch); c->scratch = nullptr; c->scratch_bytes = 0; }
   uint64_t want = bytes < (8ull << 20) ? (8ull << 20) : (bytes + (1ull << 20) - 1) & ~((1ull << 20) - 1);
   cudaError_t e = cudaMalloc(&c->scratch, want);

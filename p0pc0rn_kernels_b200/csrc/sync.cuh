@@ -36,6 +36,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   return true;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start while the
+// kernel before it in the stream still runs; it must call grid_dependency_wait() before it touches anything that kernel
+// writes (the wait returns once that kernel has finished and its writes are visible; without the attribute it returns
+// at once).  grid_launch_dependents() tells the scheduler that the kernel after this one may begin to launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // global -> shared bulk copy; both addresses 16-byte aligned, bytes a multiple of 16; completes on `bar`
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");

@@ -105,6 +105,8 @@ class Gpu:
                     except Exception: pass
             if self.opts.get("onError"): self.opts["onError"](msg)
             raise GpuError(msg)
+        if rc == -10:           # a kernel gave up on a bounded wait: a device-side failure (the context stays usable)
+            raise GpuError(msg)
         raise ValueError(msg)   # the reference throws Error(msg) for bad arguments
 
     @property
@@ -151,6 +153,18 @@ class Gpu:
         b = Buffer(self, h, int(nbytes), label)
         self.bufs.add(b)
         return b
+
+    PEER_FLAG_BYTES = 256
+
+    def peerBarrier(self, flags: Buffer, peer_flags: list, rank: int, world: int, wait_cycles: int = 0) -> None:
+        """Not in the reference: a stream-ordered barrier between the ranks of one node (p0p_peer_barrier): queue it after a
+        gemm that stored into the peers' copies of y and before the call that reads the gathered rows.  `flags`: this rank's
+        zeroed flag block (buffer(PEER_FLAG_BYTES, shareable=True)); peer_flags[r]: rank r's block opened with ipcOpen
+        (the entry at `rank` is ignored).  Every rank issues the same sequence of barriers."""
+        arr = (C.c_void_p * max(8, int(world)))()
+        for r in range(min(int(world), len(peer_flags))):
+            if r != rank and peer_flags[r] is not None: arr[r] = peer_flags[r].handle
+        self._check(lib.p0p_peer_barrier(self._h, flags.handle, arr, int(rank), int(world), int(wait_cycles)))
 
     def free(self, b):
         if b is None or b not in self.bufs:

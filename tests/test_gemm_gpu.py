@@ -283,6 +283,35 @@ CONV = [
     dict(name="conv3 pn", enc="f16", M=3 * 5 * 6, N=64, K=27 * 32, x_elems=3 * 5 * 6 * 32, w_scale=0.03, epi="bias",
          conv=dict(kind="conv3", Hi=5, Wi=6, Ci=32, Ho=5, Wo=6, stride=3, padT=0, padL=0, ks=1, pn=True)),
 ]
+# 2-D convolutions the tensor-core kernel takes (Ci % 64 == 0, whole tiles of whole output rows): the image read by tensor-map
+# boxes whose element strides are the convolution's stride, zero padding from the out-of-range fill
+CONV_TC = [
+    dict(name="tc conv3x3 c64 f16", enc="f16", M=16 * 16, N=128, K=9 * 64, x_elems=16 * 16 * 64, w_scale=0.03, epi="bias",
+         conv=dict(kind="conv", Hi=16, Wi=16, Ci=64, Ho=16, Wo=16, stride=1, padT=1, padL=1, ks=3)),
+    dict(name="tc conv3x3 stride2 c64 q4", enc="q4", M=8 * 8, N=128, K=9 * 64, x_elems=16 * 16 * 64,
+         conv=dict(kind="conv", Hi=16, Wi=16, Ci=64, Ho=8, Wo=8, stride=2, padT=1, padL=1, ks=3)),
+    dict(name="tc conv1x1 c128 q8", enc="q8", M=16 * 24, N=192, K=128, x_elems=16 * 24 * 128, epi="f32",
+         conv=dict(kind="conv", Hi=16, Wi=24, Ci=128, Ho=16, Wo=24, stride=1, padT=0, padL=0, ks=1)),
+    dict(name="tc conv5x5 pad2 c64 q8 wide image", enc="q8", M=12 * 40, N=64, K=25 * 64, x_elems=12 * 40 * 64,
+         conv=dict(kind="conv", Hi=12, Wi=40, Ci=64, Ho=12, Wo=40, stride=1, padT=2, padL=2, ks=5)),
+    dict(name="tc conv3x3 gn c64 f16", enc="f16", M=16 * 16, N=64, K=9 * 64, x_elems=16 * 16 * 64, w_scale=0.03, epi="bias",
+         conv=dict(kind="conv", Hi=16, Wi=16, Ci=64, Ho=16, Wo=16, stride=1, padT=1, padL=1, ks=3, gn=True)),
+    dict(name="tc conv3x3 stride2 unpadded c128 f16", enc="f16", M=7 * 8, N=128, K=9 * 128, x_elems=15 * 17 * 128, w_scale=0.03,
+         conv=dict(kind="conv", Hi=15, Wi=17, Ci=128, Ho=7, Wo=8, stride=2, padT=0, padL=0, ks=3)),
+    dict(name="tc conv3x3 c64 q4 320 tokens per tile", enc="q4", M=32 * 40, N=256, K=9 * 64, x_elems=32 * 40 * 64, epi="bias", res=True,
+         conv=dict(kind="conv", Hi=32, Wi=40, Ci=64, Ho=32, Wo=40, stride=1, padT=1, padL=1, ks=3)),
+]
+
+
+@pytest.mark.parametrize("case", CONV_TC, ids=lambda c: c["name"])
+def test_conv_tensor_core(gpu, oracle, case):
+    """the 2-D implicit-GEMM convolution on the tcgen05 kernel, against the oracle, and equal in kind to the CUDA-core kernel"""
+    h = CS.build(dict(case))
+    got = CS.run_gpu(gpu, h)
+    assert P()._lib.KERNEL_NAMES.get(gpu.lastKernel) == "umma", "the convolution did not take the tensor-core kernel"
+    want = CS.run_oracle(h)
+    CS.check(got, want, case["name"])
+    CS.check(CS.run_gpu(gpu, CS.build(dict(case, kernel="generic"))), want, case["name"] + " (generic)")
 
 
 @pytest.mark.parametrize("case", EXTRA + CONV, ids=lambda c: c["name"])

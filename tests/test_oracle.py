@@ -238,3 +238,30 @@ def test_golden_fixtures(oracle, name):
     out = make_golden.CASES[name](oracle)
     for k in z.files:
         assert np.array_equal(z[k], out[k]), f"{name}:{k}"
+
+
+# ---------------------------------------------------------------- statistics producers (pixstats, GroupNorm) against numpy float64
+def test_pixstats_restatement_against_numpy(oracle):
+    """src/ops/video.js:301-318: rstd per voxel over the channels"""
+    O = oracle
+    V, C = 77, 96
+    X = O.to_f16(O.randn(V * C, 3) * 2.0 + 0.5)
+    xf = O.from_f16(X).astype(np.float64).reshape(V, C)
+    np.testing.assert_allclose(O.pixstats(X, V, C, 1e-8), 1.0 / np.sqrt((xf ** 2).mean(1) + 1e-8), rtol=2e-7)
+
+
+@pytest.mark.parametrize("pix,C", [(64, 32), (200, 128), (1000, 512)])
+def test_groupnorm_restatement_against_numpy(oracle, pix, C):
+    """src/ops/misc.js:50-104: chunk partials merged by Chan's formula = the statistics of the whole tensor"""
+    O = oracle
+    X = O.to_f16(O.randn(pix * C, 5) * 1.5 + np.tile(np.linspace(-2, 2, C, dtype=np.float32), pix))
+    gamma, beta = (1.0 + O.randn(C, 6, 0.2)).astype(np.float32), O.randn(C, 7, 0.3)
+    PT = O.gn_partial(X, pix, C); nwg = -(-pix // 64)
+    pt = PT.reshape(nwg, 32, 4)
+    assert pt[:, :, 0].sum() == pix * C                                   # the counts cover every element once
+    AB = O.gn_finalize(PT, nwg, C, gamma, beta, 1e-6)
+    xf = O.from_f16(X).astype(np.float64).reshape(pix, 32, C // 32)
+    mean, var = xf.mean((0, 2)), xf.var((0, 2))
+    a = np.repeat(1.0 / np.sqrt(var + 1e-6), C // 32) * gamma
+    np.testing.assert_allclose(AB[:C], a, rtol=2e-5)
+    np.testing.assert_allclose(AB[C:], beta - np.repeat(mean, C // 32) * a, rtol=2e-4, atol=2e-5)
