@@ -69,40 +69,89 @@ __device__ __forceinline__ __half wvalue(const KP& p, uint32_t r, uint32_t k) {
 }
 
 // ---- packed conversions used by the tensor-core kernels -------------------------------------------------
-// Eight 4-bit codes of one u32 (nibble i = column 8w+i) -> four half2 in natural column order, each value
-// f16(q*s + mn) with a single rounding (HFMA2 on exact small integers).  Exact when q*s+mn fits fp32 (see
-// q4_pair_exact); the caller falls back to deq_q4 otherwise.
-__device__ __forceinline__ void q4_word_to_half2x4(uint32_t w, __half2 s2, __half2 mn2, __half2 out[4]) {
-  // byte b of w = (q[2b+1] << 4) | q[2b].  prmt builds {0x64, byte, 0x64, byte}; masking leaves
-  // lo = 0x6400 | q[2b] (= 1024 + q) and hi = 0x6400 | q[2b+1] << 4 (= 1024 + 16 q).
-  const __half2 mul = __halves2half2(__ushort_as_half(0x3c00), __ushort_as_half(0x2c00));   // (1, 1/16)
-  const __half2 sub = __halves2half2(__ushort_as_half(0xe400), __ushort_as_half(0xd400));   // (-1024, -64)
+// The conversion of a weight block is bound by instruction count (its integer and fp16 instructions issue at half rate), so
+// each tile value costs as few instructions as exactness allows.  The trick: a code is placed in the mantissa of an fp16
+// SUBNORMAL (no exponent offset to subtract afterwards) and the scale is pre-multiplied by the matching power of two, so that
+// ONE fused multiply-add per value pair yields q*s + mn with the exact product and a single rounding.
+//
+// q4.  Eight codes of one u32 (nibble i = column 8w+i) -> four half2 in natural column order.  With w4 = w << 4, byte b of w4
+// holds q[2b] in bits 4..7 and byte b of w holds q[2b+1] there; prmt pairs the two bytes and a mask leaves the halves
+// q[2b] * 2^-20 and q[2b+1] * 2^-20 (subnormals).  s20 = s * 2^20 must be finite: q4_row_fast().
+__device__ __forceinline__ void q4_word_to_half2x4(uint32_t w, __half2 s20, __half2 mn2, __half2 out[4]) {
+  const uint32_t w4 = w << 4;
 #pragma unroll
   for (int b = 0; b < 4; b++) {
-    uint32_t t = __byte_perm(w, 0x64646464u, 0x4040 | (b << 8) | b) ;   // bytes: [b, 0x64, b, 0x64] low->high
-    t &= 0x64f0640fu;
-    __half2 q = __hfma2(*reinterpret_cast<__half2*>(&t), mul, sub);      // exact integers 0..15
-    out[b] = __hfma2(q, s2, mn2);
+    uint32_t t = __byte_perm(w4, w, b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12)) & 0x00f000f0u;
+    out[b] = __hfma2(*reinterpret_cast<__half2*>(&t), s20, mn2);
   }
 }
-// Four int8 codes of one u32 (byte i = column 4w+i) -> two half2 in natural order, each f16(q*s).
-__device__ __forceinline__ void q8_word_to_half2x2(uint32_t w, __half2 s2, __half2 out[2]) {
-  uint32_t u = w ^ 0x80808080u;                       // q + 128 in 0..255
+// s * 2^20 as two exact multiplications by 2^10 (2^20 itself is not an fp16 number)
+__device__ __forceinline__ __half2 q4_scale20(__half2 s2) {
+  const __half2 k = __half2half2(__ushort_as_half(0x6400));      // 1024
+  return __hmul2(__hmul2(s2, k), k);
+}
+// true when the packed path gives f16(f32(q*s+mn)) for every code q of a (scale, min) pair:
+//  * s * 2^20 is finite (fp16 exponent field of s at most 10, i.e. s < 2^-4);
+//  * q*s+mn needs at most 24 significant bits, so that rounding it to fp32 first changes nothing: with e_s, e_m the fp16
+//    exponents, q*s spans bits e_s-10 .. e_s+4 and mn spans e_m-10 .. e_m, so e_m <= e_s + 12 and e_s <= e_m + 9 keep the sum
+//    inside 24 bits (mn == 0 is always exact).
+__device__ __forceinline__ bool q4_row_fast(uint32_t sm) {
+  uint32_t es = (sm >> 10) & 31u, em = (sm >> 26) & 31u, mm = (sm >> 16) & 0x7fffu;
+  if (es > 10u) return false;
+  if (mm == 0u) return true;
+  if (es == 0u) es = 1u;        // subnormal scale: lowest bit sits at 2^-24 either way
+  if (em == 0u) em = 1u;
+  return em <= es + 12u && es <= em + 9u;
+}
+// one row of a q4 record (32 k: four code words, sm = scale | min << 16) -> 16 half2, every value f16(f32(q*s+mn)).  The
+// packed path serves almost every row; a lane whose (scale, min) pair fails the test redoes its row in fp32 (a divergent
+// branch that is almost never taken; the warp is converged again on return).
+__device__ __forceinline__ void q4_row32(const uint32_t (&w)[4], uint32_t sm, __half2 (&v)[16]) {
+  const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+  const __half2 s20 = q4_scale20(s2);
+#pragma unroll
+  for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s20, m2, v + 4 * i);
+  if (!q4_row_fast(sm)) {
+    const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+  }
+  __syncwarp();
+}
+
+// q8.  Four int8 codes of one u32 (byte i = column 4w+i) -> two half2 in natural order, each f16(q*s).  u = q + 128 is placed
+// as a subnormal u * 2^-24 (prmt with a zero register), s24 = s * 2^24, and the fused multiply-add adds -128*s: the result
+// (u - 128) * s = q * s is exact before its single rounding.  s24 must be finite: q8_row_fast().
+__device__ __forceinline__ void q8_word_to_half2x2(uint32_t w, __half2 s24, __half2 off, __half2 out[2]) {
+  const uint32_t u = w ^ 0x80808080u;                       // q + 128 in 0..255
+  uint32_t a = __byte_perm(u, 0u, 0x4140);                  // [b0, 0, b1, 0]
+  uint32_t b = __byte_perm(u, 0u, 0x4342);                  // [b2, 0, b3, 0]
+  out[0] = __hfma2(*reinterpret_cast<__half2*>(&a), s24, off);
+  out[1] = __hfma2(*reinterpret_cast<__half2*>(&b), s24, off);
+}
+// the same for any scale: (u + 1024 as the pattern 0x6400 | u) - 1152 = q, then one multiplication
+__device__ __forceinline__ void q8_word_to_half2x2_any(uint32_t w, __half2 s2, __half2 out[2]) {
+  uint32_t u = w ^ 0x80808080u;
   const __half2 off = __half2half2(__ushort_as_half(0xe480));   // -1152 = -(1024 + 128)
   uint32_t a = __byte_perm(u, 0x64646464u, 0x4140);   // [b0, 0x64, b1, 0x64]
   uint32_t b = __byte_perm(u, 0x64646464u, 0x4342);   // [b2, 0x64, b3, 0x64]
   out[0] = __hmul2(__hadd2(*reinterpret_cast<__half2*>(&a), off), s2);
   out[1] = __hmul2(__hadd2(*reinterpret_cast<__half2*>(&b), off), s2);
 }
-// true when f16(q*s+mn) by one HFMA equals f16(f32(q*s+mn)) for every code q: the exact sum needs at most 24
-// significant bits: with e_s, e_m the fp16 exponents, q*s spans bits e_s-10 .. e_s+4 and mn spans e_m-10 .. e_m,
-// so e_m <= e_s + 12 and e_s <= e_m + 9 keep the sum inside 24 bits (mn == 0 is always exact).
-__device__ __forceinline__ bool q4_pair_exact(uint32_t sm) {
-  uint32_t es = (sm >> 10) & 31u, em = (sm >> 26) & 31u, mm = (sm >> 16) & 0x7fffu;
-  if (mm == 0u) return true;
-  if (es == 0u) es = 1u;        // subnormal scale: lowest bit sits at 2^-24 either way
-  if (em == 0u) em = 1u;
-  return em <= es + 12u && es <= em + 9u;
+__device__ __forceinline__ bool q8_row_fast(uint32_t s_bits) { return ((s_bits >> 10) & 31u) <= 6u; }      // s < 2^-8: s * 2^24 is finite
+// NW code words of one row (4 codes each; a row of a q8 record is 16 words) -> 2 * NW half2, every value f16(q*s)
+template <int NW>
+__device__ __forceinline__ void q8_row(const uint32_t (&w)[NW], uint32_t s_bits, __half2 (&v)[2 * NW]) {
+  const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)s_bits));
+  if (__all_sync(0xffffffffu, q8_row_fast(s_bits))) {           // scales of one tensor are of one magnitude: the vote is all but always true
+    const __half2 k = __half2half2(__ushort_as_half(0x6c00));   // 4096: s * 2^24 as two exact multiplications by 2^12
+    const __half2 s24 = __hmul2(__hmul2(s2, k), k), off = __hmul2(s2, __half2half2(__ushort_as_half(0xd800)));      // -128 * s
+#pragma unroll
+    for (int i = 0; i < NW; i++) q8_word_to_half2x2(w[i], s24, off, v + 2 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < NW; i++) q8_word_to_half2x2_any(w[i], s2, v + 2 * i);
+  }
 }
 
 }  // namespace p0p

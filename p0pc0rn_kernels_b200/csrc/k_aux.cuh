@@ -7,11 +7,12 @@ namespace p0p {
 
 // One thread per (row, 32-column group): writes f16 tile values row-major [nr][cols].
 // path 0: fp32 fma + one rounding per value.  path 1: the packed half2 conversion of the tensor-core kernels
-// (with its per-row exactness test and fallback).
+// (q4_row32 / q8_row of common.cuh, with their exactness tests and fallbacks).
 __global__ void k_dequant(uint32_t enc, const uint8_t* __restrict__ W, uint32_t wG, uint32_t cols, uint32_t r0, uint32_t nr, uint32_t path, __half* __restrict__ out) {
   const uint32_t groups = cols / 32u;
-  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (size_t)nr * groups) return;
+  const size_t n = (size_t)nr * groups, idx0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx0 < n;
+  const size_t idx = live ? idx0 : n - 1u;        // surplus threads repeat the last item (the conversions are whole-warp operations) and store nothing
   const uint32_t lr = (uint32_t)(idx / groups), g = (uint32_t)(idx % groups), r = r0 + lr, rr = r & 63u;
   __half2 v[16];
   if (enc == P0P_ENC_Q4) {
@@ -19,11 +20,8 @@ __global__ void k_dequant(uint32_t enc, const uint8_t* __restrict__ W, uint32_t 
     const uint4 q = __ldg(reinterpret_cast<const uint4*>(rec + rr * 16u));
     const uint32_t sm = ldg32(rec + 1024u + rr * 4u);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    if (path == 1u && q4_pair_exact(sm)) {
-      const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
-#pragma unroll
-      for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
-    } else {
+    if (path == 1u) q4_row32(w, sm, v);
+    else {
       const float s = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
 #pragma unroll
       for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, s, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, s, mn));
@@ -33,13 +31,10 @@ __global__ void k_dequant(uint32_t enc, const uint8_t* __restrict__ W, uint32_t 
     const uint4* cp = reinterpret_cast<const uint4*>(rec + rr * 64u + (g & 1u) * 32u);
     const uint4 qa = __ldg(cp), qb = __ldg(cp + 1);
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    const __half hs = __ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(rec + 4096u + rr * 2u)));
-    if (path == 1u) {
-      const __half2 s2 = __half2half2(hs);
-#pragma unroll
-      for (int i = 0; i < 8; i++) q8_word_to_half2x2(w[i], s2, v + 2 * i);
-    } else {
-      const float s = __half2float(hs);
+    const unsigned short hsb = __ldg(reinterpret_cast<const unsigned short*>(rec + 4096u + rr * 2u));
+    if (path == 1u) q8_row<8>(w, hsb, v);
+    else {
+      const float s = __half2float(__ushort_as_half(hsb));
 #pragma unroll
       for (int i = 0; i < 16; i++) {
         const uint32_t x = w[i >> 1] >> (16 * (i & 1));
@@ -51,6 +46,7 @@ __global__ void k_dequant(uint32_t enc, const uint8_t* __restrict__ W, uint32_t 
 #pragma unroll
     for (int i = 0; i < 16; i++) v[i] = __halves2half2(__ushort_as_half(__ldg(rp + 2 * i)), __ushort_as_half(__ldg(rp + 2 * i + 1)));
   }
+  if (!live) return;
   __half2* o = reinterpret_cast<__half2*>(out + (size_t)lr * cols + g * 32u);
 #pragma unroll
   for (int i = 0; i < 16; i++) o[i] = v[i];

@@ -55,7 +55,10 @@ struct UmmaP {
   uint32_t BT;          // tokens per tile: a multiple of 16 up to 256 (one UMMA of N = BT), or of 32 up to 384 (two of N = BT / 2)
   uint32_t NACC;        // accumulators: 2 (the next tile's multiply overlaps the epilogue) or 1 (wide tiles: tensor memory holds one)
   uint32_t KSPLIT;      // accumulators per tile that take the 16-k multiplies in turn (1, 2 or 4), summed by the epilogue
-  uint32_t NS;          // operand stages (3 or 4)
+  uint32_t NS;          // stages of the token ring (2 .. 8)
+  uint32_t KW;          // k-steps of 64 k per pipeline step (1 or 2)
+  uint32_t NA;          // stages of the dequantised operand in tensor memory (NA * KW <= 4); fp16 weights: = NS
+  uint32_t LOCK;        // 1: the token ring and the operand ring advance together and share their barriers (NA == NS)
   uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
   uint32_t G;           // token tiles per group of the tile order (tile_coords)
@@ -119,32 +122,55 @@ struct Ring {
 // EPI: the fused epilogue, a compile-time constant.  One instantiation per (encoding, epilogue): a kernel that carries
 // all seven epilogues is ~470 KB of code, most of it never run by a given launch.
 constexpr uint32_t U_ACC_STRIDE_ATM = 192, U_A_COL0_ATM = 384;
-constexpr uint32_t U_DEQ_WARPS = 8;
-template <int ENC, int EPI>
+constexpr uint32_t U_DEQ_WARPS = 8;      // two groups of four
+constexpr uint32_t U_NX_MAX = 8;         // most stages of the token ring
+// Pipeline steps.  One step covers KW k-steps of 64 k (KW = 1 or 2, chosen per launch): every hand-over between the roles - a
+// barrier wait, a fence, a commit, a trip round a warp's loop - costs a few hundred cycles of single-warp latency, which for
+// narrow and medium tiles is more than the multiplies of 64 k take, so those tiles move 128 k per hand-over.
+// Three producers feed the multiply, each through a ring of stages with a "ready" and a "free" mbarrier per stage:
+//   X  token tiles (and fp16 weight tiles), NS stages of shared memory of KW sub-tiles each, filled by TMA;
+//   Q  quantised records, NQ stages of shared memory, filled by bulk copies (KSUP k-steps each, a multiple of KW);
+//   A  dequantised weight operand: NA stages of KW 32-column sub-stages of tensor memory (NA * KW <= 4), filled by the
+//      dequantisation warps.
+// Wide tiles are bound by the multiplies, and there every instruction the issuing warp runs between two multiplies shows in the
+// total: X and A then advance in lock step (NA = NS) and SHARE their barriers - one wait and one commit per step.  Narrow tiles
+// are bound by the hand-overs instead; their token tiles are small, so the X ring gets its own barriers and more stages than
+// tensor memory has operand stages (the load of a tile is only issued once its stage is free, and with few stages that round
+// trip would be exposed).
+// Dequantisation: two groups of four warps; a thread converts one whole operand row (64 k).  KW = 1: the groups take the steps in
+// turn.  KW = 2: group g converts sub-step g of every step, so both groups fill the same stage side by side.  The warps that
+// wait are parked by the hardware (mbar_try), not spinning beside the ones that work.
+// KW and LOCK are compile-time (three variants exist: (1, lock), (2, lock), (2, separate)): the issuing warp's loop is the
+// critical path of wide tiles and must not carry run-time choices.
+template <int ENC, int EPI, int KW_, bool LOCK_>
 __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW) {
   extern __shared__ unsigned char smem_raw[];
   constexpr bool ATM = ENC != P0P_ENC_F16;
+  constexpr uint32_t KW = KW_;
+  constexpr bool lock = LOCK_;
   const KP& p = u.p;
   const uint32_t BT = u.BT, NS = u.NS, NQ = u.NQ;
   const uint32_t HB = BT > 256u ? BT / 2u : BT, NH = BT > 256u ? 2u : 1u;          // tokens per UMMA / TMA box, and how many of them make a tile
   const bool two_acc = u.NACC == 2u;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                     // operand tiles need 1024-byte alignment
   unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * BT * 128u;
+  const uint32_t XT = BT * 128u, XS = KW * XT;                                     // bytes of a token sub-tile (64 k) and of a stage
+  const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * XS;
   const uint32_t acc_stride = ATM ? U_ACC_STRIDE_ATM : 256u;
   const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * UQ<ENC>::STAGE);
   const uint32_t bars = epi_sh + (uint32_t)U_EPI_BYTES;
   float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
-  // barrier slots (8 bytes each): operands of a stage ready / stage free / record stage ready / record stage free / accumulator ready / free
-  const uint32_t full = bars, empty = full + 8u * 4u, wq_full = empty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ_MAX;
+  // barrier slots (8 bytes each)
+  const uint32_t xfull = bars, xempty = xfull + 8u * U_NX_MAX, afull = xempty + 8u * U_NX_MAX, aempty = afull + 8u * 4u;
+  const uint32_t wq_full = aempty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ_MAX;
   const uint32_t acc_full = wq_empty + 8u * U_NQ_MAX, acc_empty = acc_full + 16u, tmem_slot = acc_empty + 16u;
+  const uint32_t NA = u.NA;                                                       // operand stage of step g: g % NA, its parity: (g / NA) & 1
+  const uint32_t pfull = lock ? afull : xfull, pempty = lock ? aempty : xempty;   // the barriers the token producer works with
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   if (tid == 0) {
-    for (uint32_t s = 0; s < 4u; s++) {
-      mbar_init(full + 8u * s, ENC == P0P_ENC_F16 ? 1u : 1u + U_DEQ_WARPS);     // the producer's expect_tx arrival (+ the dequantisation warps)
-      mbar_init(empty + 8u * s, 1u);
-    }
+    for (uint32_t s = 0; s < U_NX_MAX; s++) { mbar_init(xfull + 8u * s, 1u); mbar_init(xempty + 8u * s, 1u); }      // the producer's expect_tx arrival / the multiplies' commit
+    for (uint32_t s = 0; s < 4u; s++) { mbar_init(afull + 8u * s, (ATM ? 4u * KW : 0u) + (lock ? 1u : 0u)); mbar_init(aempty + 8u * s, 1u); }       // the dequantisation warps of a step (+ the token producer) / the commit
     for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, U_DEQ_WARPS); }
     for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
     fence_mbar_init();
@@ -163,36 +189,41 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     if (lane == 0) {
       Ring r(NS);
       bool ok = true;
+      const uint32_t nap = BT <= 64u ? 32u : 200u;                     // narrow tiles turn over quickly: poll their stages often
       for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
         const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t tile = un.tile, kb = un.kb, ke = un.ke;
         uint32_t nt, mt; tile_coords(u, tile, nt, mt);
-        for (uint32_t ks = kb; ks < ke; ks++, r.next()) {
-          if (!mbar_wait(empty + 8u * r.s, r.ph ^ 1u, u.status, 201, 200u)) { ok = false; break; }
-          mbar_expect_tx(full + 8u * r.s, BT * 128u + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u));
-          if (p.xmode == P0P_X_CONV3) {
-            // implicit GEMM (src/ops/gemm.js:68-80): the 64 k of this step are channels c0.. of ONE tap (kt, ky, kx); the tile's
-            // tokens are cvR whole rows of one output frame, so their inputs are a box of the clip shifted by the tap, and
-            // what falls outside the image reads as zero.  Frame index: clamp to the clip, then ring slot or chunk offset.
-            const uint32_t tpf = p.Ho / u.cvR, ot = mt / tpf, oy0 = (mt - ot * tpf) * u.cvR;
-            const uint32_t kg = ks * 64u, tap = kg / p.Ci, c0 = kg - tap * p.Ci, kt = tap / 9u, ky = (tap / 3u) % 3u, kx = tap % 3u;
-            const int itg = min(max((int)(ot + p.padT + kt) - 1, 0), (int)p.stride - 1);
-            const int it = p.ks > 1u ? itg % (int)p.ks : itg - (int)p.padL;
-            const uint32_t rb = u.cvR / NH;
-            for (uint32_t h = 0; h < NH; h++)
-              tma_load_4d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)c0, (int)kx - 1, (int)(oy0 + h * rb + ky) - 1, it, full + 8u * r.s);
-          } else if (p.xmode == P0P_X_CONV) {
-            // 2-D implicit GEMM (src/ops/gemm.js:81-91): the tile's tokens are cvR whole output rows; the 64 k of this step are
-            // channels c0.. of one tap (ky, kx) = (tap / ks, tap % ks).  The tensor map's element strides walk the input by the
-            // convolution's stride, so output (oy, ox) reads input (oy * stride + ky - padT, ox * stride + kx - padL): the box
-            // starts at the first output row / column's input position and what falls outside the image reads as zero.
-            const uint32_t oy0 = mt * u.cvR;
-            const uint32_t kg = ks * 64u, tap = kg / p.Ci, c0 = kg - tap * p.Ci, ky = tap / p.ks, kx = tap - ky * p.ks;
-            const uint32_t rb = u.cvR / NH;
-            for (uint32_t h = 0; h < NH; h++)
-              tma_load_4d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)c0, (int)kx - (int)p.padL, (int)((oy0 + h * rb) * p.stride + ky) - (int)p.padT, 0, full + 8u * r.s);
-          } else
-            for (uint32_t h = 0; h < NH; h++) tma_load_2d(x_st + r.s * BT * 128u + h * HB * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT + h * HB), full + 8u * r.s);
-          if (ENC == P0P_ENC_F16) tma_load_2d(a_st + r.s * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), full + 8u * r.s);
+        for (uint32_t k0 = kb; k0 < ke; k0 += KW, r.next()) {
+          const uint32_t cnt = min(KW, ke - k0);
+          if (!mbar_wait(pempty + 8u * r.s, r.ph ^ 1u, u.status, 201, nap)) { ok = false; break; }
+          mbar_expect_tx(pfull + 8u * r.s, cnt * (XT + (ENC == P0P_ENC_F16 ? U_A_BYTES : 0u)));
+          for (uint32_t j = 0; j < cnt; j++) {
+            const uint32_t ks = k0 + j, dst = x_st + r.s * XS + j * XT;
+            if (p.xmode == P0P_X_CONV3) {
+              // implicit GEMM (src/ops/gemm.js:68-80): the 64 k of this k-step are channels c0.. of ONE tap (kt, ky, kx); the tile's
+              // tokens are cvR whole rows of one output frame, so their inputs are a box of the clip shifted by the tap, and
+              // what falls outside the image reads as zero.  Frame index: clamp to the clip, then ring slot or chunk offset.
+              const uint32_t tpf = p.Ho / u.cvR, ot = mt / tpf, oy0 = (mt - ot * tpf) * u.cvR;
+              const uint32_t kg = ks * 64u, tap = kg / p.Ci, c0 = kg - tap * p.Ci, kt = tap / 9u, ky = (tap / 3u) % 3u, kx = tap % 3u;
+              const int itg = min(max((int)(ot + p.padT + kt) - 1, 0), (int)p.stride - 1);
+              const int it = p.ks > 1u ? itg % (int)p.ks : itg - (int)p.padL;
+              const uint32_t rb = u.cvR / NH;
+              for (uint32_t h = 0; h < NH; h++)
+                tma_load_4d(dst + h * HB * 128u, &mapX, (int)c0, (int)kx - 1, (int)(oy0 + h * rb + ky) - 1, it, pfull + 8u * r.s);
+            } else if (p.xmode == P0P_X_CONV) {
+              // 2-D implicit GEMM (src/ops/gemm.js:81-91): the tile's tokens are cvR whole output rows; the 64 k of this k-step are
+              // channels c0.. of one tap (ky, kx) = (tap / ks, tap % ks).  The tensor map's element strides walk the input by the
+              // convolution's stride, so output (oy, ox) reads input (oy * stride + ky - padT, ox * stride + kx - padL): the box
+              // starts at the first output row / column's input position and what falls outside the image reads as zero.
+              const uint32_t oy0 = mt * u.cvR;
+              const uint32_t kg = ks * 64u, tap = kg / p.Ci, c0 = kg - tap * p.Ci, ky = tap / p.ks, kx = tap - ky * p.ks;
+              const uint32_t rb = u.cvR / NH;
+              for (uint32_t h = 0; h < NH; h++)
+                tma_load_4d(dst + h * HB * 128u, &mapX, (int)c0, (int)kx - (int)p.padL, (int)((oy0 + h * rb) * p.stride + ky) - (int)p.padT, 0, pfull + 8u * r.s);
+            } else
+              for (uint32_t h = 0; h < NH; h++) tma_load_2d(dst + h * HB * 128u, &mapX, (int)(ks * 64u), (int)(mt * BT + h * HB), pfull + 8u * r.s);
+            if (ENC == P0P_ENC_F16) tma_load_2d(a_st + (r.s * KW + j) * U_A_BYTES, &mapW, (int)(ks * 64u), (int)(p.wR0 + nt * 128u), pfull + 8u * r.s);
+          }
         }
       }
     }
@@ -213,7 +244,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         const unsigned char* src1 = p.W + ((size_t)trow[1] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
         for (uint32_t ks = kb; ks < ke; ks += UQ<ENC>::KSUP, q.next()) {
           const uint32_t bytes = min(UQ<ENC>::KSUP, ke - ks) * UQ<ENC>::RB;
-          if (!mbar_wait(wq_empty + 8u * q.s, q.ph ^ 1u, u.status, 202, 500u)) { ok = false; break; }
+          if (!mbar_wait(wq_empty + 8u * q.s, q.ph ^ 1u, u.status, 202, 200u)) { ok = false; break; }
           mbar_expect_tx(wq_full + 8u * q.s, 2u * bytes);
           bulk_g2s(q_st + q.s * UQ<ENC>::STAGE, src0 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
           bulk_g2s(q_st + q.s * UQ<ENC>::STAGE + UQ<ENC>::KSUP * UQ<ENC>::RB + 64u, src1 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
@@ -226,7 +257,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     // instruction takes; inside a one-lane branch every operand of every tcgen05.mma is first moved there, which
     // costs more than the multiply itself.
     const uint32_t idesc = umma_idesc_f16(128u, HB);
-    Ring r(NS);
+    Ring r(NS), ar(NA);
     uint32_t tl = 0;
     bool ok = true;
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x, tl++) {
@@ -235,28 +266,42 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
       if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + 8u * buf, par ^ 1u, u.status, 203, 100u))) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * acc_stride;
-      for (uint32_t ks = kb; ks < ke; ks++, r.next()) {
-        if (!__all_sync(0xffffffffu, mbar_wait(full + 8u * r.s, r.ph, u.status, 204))) { ok = false; break; }
+      for (uint32_t k0 = kb; k0 < ke; k0 += KW, r.next(), ar.next()) {
+        const uint32_t as = ar.s, cnt = min(KW, ke - k0);
+        bool rdy = lock || mbar_wait(xfull + 8u * r.s, r.ph, u.status, 204);
+        if (ATM || lock) rdy = rdy && mbar_wait(afull + 8u * as, ar.ph, u.status, 205);
+        if (!__all_sync(0xffffffffu, rdy)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t bd = umma_desc_sw128(x_st + r.s * BT * 128u);
-        const uint32_t at = tmem_base + U_A_COL0_ATM + r.s * 32u;
-        const uint64_t ad = umma_desc_sw128(a_st + r.s * U_A_BYTES);
-        const uint32_t first = ks - kb;                             // 0 on the unit's first k-step: the first multiply overwrites
+        // (operands computed in warp-uniform control flow: they stay in uniform registers, which is what the instruction takes)
+        uint64_t bd[KW], ad[KW]; uint32_t at[KW];
+#pragma unroll
+        for (uint32_t j = 0; j < KW; j++) {
+          bd[j] = umma_desc_sw128(x_st + r.s * XS + j * XT);
+          at[j] = tmem_base + U_A_COL0_ATM + (as * KW + j) * 32u;
+          ad[j] = umma_desc_sw128(a_st + (r.s * KW + j) * U_A_BYTES);
+        }
+        const uint32_t first = k0 - kb;                             // 0 on the unit's first k-step: the first multiply overwrites
         if (elect_one()) {
 #pragma unroll
-          for (uint32_t kk = 0; kk < 4u; kk++) {                      // per 16 k: 8 tensor-memory columns / +32 bytes
-            // consecutive multiplies into ONE accumulator start ~180 cycles apart whatever their width; into different
-            // accumulators ~35.  Narrow tiles therefore rotate over KSPLIT accumulators (wide ones over their two halves).
-            const uint32_t dk = d_tmem + (kk & (u.KSPLIT - 1u)) * BT, accum = first | (kk >= u.KSPLIT ? 1u : 0u);
-            if (ATM) {
-              umma_f16_ts(dk, at + 8u * kk, bd + 2u * kk, idesc, accum);
-              if (NH == 2u) umma_f16_ts(dk + HB, at + 8u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
-            } else {
-              umma_f16_ss(dk, ad + 2u * kk, bd + 2u * kk, idesc, accum);
-              if (NH == 2u) umma_f16_ss(dk + HB, ad + 2u * kk, bd + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
+          for (uint32_t j = 0; j < KW; j++) {
+            if (j < cnt) {
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4u; kk++) {                  // per 16 k: 8 tensor-memory columns / +32 bytes
+                // consecutive multiplies into ONE accumulator start ~180 cycles apart whatever their width; into different
+                // accumulators ~35.  Narrow tiles therefore rotate over KSPLIT accumulators (wide ones over their two halves).
+                const uint32_t dk = d_tmem + (kk & (u.KSPLIT - 1u)) * BT, accum = first | j | (kk >= u.KSPLIT ? 1u : 0u);
+                if (ATM) {
+                  umma_f16_ts(dk, at[j] + 8u * kk, bd[j] + 2u * kk, idesc, accum);
+                  if (NH == 2u) umma_f16_ts(dk + HB, at[j] + 8u * kk, bd[j] + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
+                } else {
+                  umma_f16_ss(dk, ad[j] + 2u * kk, bd[j] + 2u * kk, idesc, accum);
+                  if (NH == 2u) umma_f16_ss(dk + HB, ad[j] + 2u * kk, bd[j] + ((HB * 128u) >> 4) + 2u * kk, idesc, accum);
+                }
+              }
             }
           }
-          umma_commit(empty + 8u * r.s);
+          if (!lock) umma_commit(xempty + 8u * r.s);
+          if (ATM || lock) umma_commit(aempty + 8u * as);
         }
         __syncwarp();
       }
@@ -303,55 +348,73 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     }
   } else if (ENC != P0P_ENC_F16 && warp < 6u + U_DEQ_WARPS) {
     // ================================================================= dequantisation: codes -> fp16 operand rows in tensor
-    // memory.  All eight warps work on every k-step: thread = (weight row r of the block's 128, half hk of the step's 64 k).
-    // A warp reaches the tensor-memory lanes 32 * (warp % 4) .. + 31, which fixes its rows; warps 6..9 take k 0..31 of
-    // the step (operand columns 0..15), warps 10..13 take k 32..63 (columns 16..31).
-    const uint32_t hk = (warp - 6u) >> 2, r = (warp & 3u) * 32u + lane;
+    // memory.  A warp reaches the tensor-memory lanes 32 * (warp % 4) .. + 31, which fixes its 32 weight rows; a thread
+    // converts one whole operand row (64 k) of a k-step.  The loop runs over record stages (KSUP k-steps, i.e. KSUP / KW pipeline
+    // steps); inside a stage a group visits its own k-steps: those of its parity in the running count of steps (KW = 1), or
+    // sub-step `grp` of every step (KW = 2; a step whose second sub-step does not exist still gets group 1's arrival).
+    const uint32_t r = (warp & 3u) * 32u + lane, grp = (warp - 6u) >> 2;
     const uint32_t tsel = swiglu ? (r & 1u) : (r >> 6), rr = swiglu ? (r >> 1) : (r & 63u);
     const uint32_t tile_off = tsel * (UQ<ENC>::KSUP * UQ<ENC>::RB + 64u);
-    // q4: a k-step is two records (32 k each), this thread reads its row in record hk; q8: one record, this thread reads 32 of its row's 64 codes
-    const uint32_t rec_row = tile_off + (ENC == P0P_ENC_Q4 ? hk * 1280u + rr * 16u : rr * 64u + hk * 32u);
-    const uint32_t rec_sm = tile_off + (ENC == P0P_ENC_Q4 ? hk * 1280u + 1024u + rr * 4u : 4096u + rr * 2u);
-    const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM + hk * 16u;
-    Ring ar(NS), qr(NQ);
-    uint32_t sub = 0;
+    const uint32_t rec_row = tile_off + (ENC == P0P_ENC_Q4 ? rr * 16u : rr * 64u);
+    const uint32_t rec_sm = tile_off + (ENC == P0P_ENC_Q4 ? 1024u + rr * 4u : 4096u + rr * 2u);
+    const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM;
+    const uint32_t sub = KW == 2u ? grp : 0u, stride = KW == 2u ? 1u : 2u;
+    // this group's steps are every `stride`-th of the running count of steps; their operand stage walks the ring of NA with them
+    uint32_t as = KW == 2u ? 0u : grp, aph = 0u;
+    Ring qr(NQ);
+    uint32_t gpar = 0;                                             // parity of the count of steps before this record stage (KW = 1)
     bool ok = true;
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-      const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t kb = un.kb, ke = un.ke;
-      for (uint32_t ks = kb; ks < ke; ks++, ar.next()) {
-        const bool last_sub = sub == UQ<ENC>::KSUP - 1u || ks == ke - 1u;
-        // the record stage is awaited at its first k-step only; the operand stage must have been read by the multiplies that used it last
-        if ((sub == 0u && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(empty + 8u * ar.s, ar.ph ^ 1u, u.status, 208)) { ok = false; break; }
-        const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + sub * UQ<ENC>::RB;
-        __half2 v[16];
-        if (ENC == P0P_ENC_Q4) {
-          const uint4 cq = u_lds128(rec + rec_row);
-          const uint32_t sm = u_lds32(rec + rec_sm);
-          const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
-          const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sm & 0xffffu))), m2 = __half2half2(__ushort_as_half((unsigned short)(sm >> 16)));
+      const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t n = un.ke - un.kb;
+      for (uint32_t j0 = 0; j0 < n && ok; j0 += UQ<ENC>::KSUP, qr.next()) {
+        const uint32_t cnt = min(UQ<ENC>::KSUP, n - j0);
+        bool fresh = true;                                         // the record stage is awaited at this group's first k-step in it
+        // k-step jj of the record stage is this group's when jj % 2 == grp (KW = 2: sub-step grp of a step) or when the running
+        // count of k-steps has the group's parity (KW = 1).  KW = 2 with an odd tail: group 1 passes the missing sub-step once,
+        // only to arrive (after the same wait for the free stage as any arrival).
+        const uint32_t jfirst = KW == 2u ? grp : (grp ^ gpar);
+        const uint32_t jend = cnt + (KW == 2u ? (grp & cnt & 1u) : 0u);
+        for (uint32_t jj = jfirst; jj < jend; jj += 2u) {
+          const bool have = jj < cnt;
+          if ((have && fresh && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(aempty + 8u * as, aph ^ 1u, u.status, 208)) { ok = false; break; }
+          if (have) {
+            fresh = false;
+            const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + jj * UQ<ENC>::RB;
+            const uint32_t ta = ta0 + (as * KW + sub) * 32u;
+            if (ENC == P0P_ENC_Q4) {
+              // both 32-k halves of the row are fetched first, so that the second half's loads are in flight while the first converts
+              const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 1280u);
+              const uint32_t sm0 = u_lds32(rec + rec_sm), sm1 = u_lds32(rec + rec_sm + 1280u);
+              const uint32_t w0[4] = {c0.x, c0.y, c0.z, c0.w}, w1[4] = {c1.x, c1.y, c1.z, c1.w};
+              __half2 v[16];
+              q4_row32(w0, sm0, v);
+              tmem_st16(ta, *reinterpret_cast<const uint32_t(*)[16]>(v));
+              q4_row32(w1, sm1, v);
+              tmem_st16(ta + 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
+            } else {
+              const uint32_t sb = u_lds16(rec + rec_sm);
 #pragma unroll
-          for (int i = 0; i < 4; i++) q4_word_to_half2x4(w[i], s2, m2, v + 4 * i);
-          // the packed path is exact for almost every (scale, minimum) pair; a lane whose pair fails the test redoes its row in
-          // fp32 (a divergent branch that is almost never taken, instead of a vote that every k-step would wait for)
-          if (!q4_pair_exact(sm)) {
-            const float sc = __half2float(__ushort_as_half((unsigned short)(sm & 0xffffu))), mn = __half2float(__ushort_as_half((unsigned short)(sm >> 16)));
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = __halves2half2(deq_q4((w[i >> 2] >> (8 * (i & 3))) & 15u, sc, mn), deq_q4((w[i >> 2] >> (8 * (i & 3) + 4)) & 15u, sc, mn));
+              for (uint32_t h = 0; h < 2u; h++) {
+                const uint4 c0 = u_lds128(rec + rec_row + h * 32u), c1 = u_lds128(rec + rec_row + h * 32u + 16u);
+                const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                __half2 v[16];
+                q8_row<8>(w, sb, v);
+                tmem_st16(ta + h * 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
+              }
+            }
+            tmem_st_wait(); tc_fence_before();                      // tensor-memory stores done and ordered before the MMA warp's read
           }
           __syncwarp();
-        } else {
-          const __half2 s2 = __half2half2(__ushort_as_half(u_lds16(rec + rec_sm)));
-          const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 16u);
-          const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-          for (int i = 0; i < 8; i++) q8_word_to_half2x2(w[i], s2, v + 2 * i);
+          if (lane == 0) mbar_arrive(afull + 8u * as);
+          as += stride; if (as >= NA) { as -= NA; aph ^= 1u; }
         }
-        tmem_st16(ta0 + ar.s * 32u, *reinterpret_cast<const uint32_t(*)[16]>(v));
-        tmem_st_wait(); tc_fence_before();                        // tensor-memory stores done and ordered before the MMA warp's read
+        gpar ^= cnt & 1u;
+        // Every warp releases every record stage once, after its last k-step there.  A group with no k-step of its own in the
+        // stage still waits for the stage to be filled first: its release must not land in the barrier phase of the stage's
+        // previous contents.
+        if (ok && fresh && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 209)) { ok = false; break; }
         __syncwarp();
-        if (lane == 0) mbar_arrive(full + 8u * ar.s);
-        // every warp uses every record stage and releases it after its last k-step there
-        if (last_sub) { if (lane == 0) mbar_arrive(wq_empty + 8u * qr.s); qr.next(); sub = 0; } else sub++;
+        if (lane == 0) mbar_arrive(wq_empty + 8u * qr.s);
       }
     }
   }
@@ -385,14 +448,16 @@ __global__ void __launch_bounds__(128) k_umma_finish(const UmmaP u) {
   epilogue_cols<U_EPI_TB, EPI>(p, m0, nt * 128u, c, acc, sh, 1, epilogue_vec_ok(p), 0u);
 }
 
-// ---- the instantiations live in three translation units (umma_q4.cu, umma_q8.cu, umma_f16.cu); these tables find them
+// ---- the instantiations live in three translation units (umma_q4.cu, umma_q8.cu, umma_f16.cu); these tables find them.
+// variant: 0 = (KW 1, lock step), 1 = (KW 2, lock step), 2 = (KW 2, separate token ring); fp16 weights have variant 0 only.
 typedef void (*umma_kernel_fn)(const UmmaP, const CUtensorMap, const CUtensorMap);
 typedef void (*umma_finish_fn)(const UmmaP);
-umma_kernel_fn umma_kernel_q4(uint32_t epi);
-umma_kernel_fn umma_kernel_q8(uint32_t epi);
+umma_kernel_fn umma_kernel_q4(uint32_t variant, uint32_t epi);
+umma_kernel_fn umma_kernel_q8(uint32_t variant, uint32_t epi);
 umma_kernel_fn umma_kernel_f16(uint32_t epi);
 umma_finish_fn umma_finish_kernel(uint32_t epi);
-#define P0P_UMMA_TABLE(ENC) {k_gemm_umma<ENC, P0P_EPI_F16>, k_gemm_umma<ENC, P0P_EPI_F32>, k_gemm_umma<ENC, P0P_EPI_RESADD>, k_gemm_umma<ENC, P0P_EPI_SWIGLU>, \
-                             k_gemm_umma<ENC, P0P_EPI_HEADS>, k_gemm_umma<ENC, P0P_EPI_BIAS>, k_gemm_umma<ENC, P0P_EPI_ONORMGATE>}
+#define P0P_UMMA_ROW(ENC, KW, LOCK) {k_gemm_umma<ENC, P0P_EPI_F16, KW, LOCK>, k_gemm_umma<ENC, P0P_EPI_F32, KW, LOCK>, k_gemm_umma<ENC, P0P_EPI_RESADD, KW, LOCK>, \
+                                     k_gemm_umma<ENC, P0P_EPI_SWIGLU, KW, LOCK>, k_gemm_umma<ENC, P0P_EPI_HEADS, KW, LOCK>, k_gemm_umma<ENC, P0P_EPI_BIAS, KW, LOCK>, \
+                                     k_gemm_umma<ENC, P0P_EPI_ONORMGATE, KW, LOCK>}
 
 }  // namespace p0p

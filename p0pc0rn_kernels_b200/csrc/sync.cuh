@@ -17,14 +17,16 @@ __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+// One try: the hardware parks the thread for a short, system-chosen time unless the phase completes first.  (An explicit, longer
+// suspend-time hint was measured: the waiters then wake late and every kernel here got 10-20 % slower.)
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// bounded wait; false after the limit (the code lands in *status).  sleep_ns > 0: the thread backs off between
-// polls, for waits that are long and off the critical path (a polling warp otherwise takes issue slots from the
-// warps that work).  The clock is read only every 256 polls.
+// bounded wait; false after the limit (the code lands in *status).  sleep_ns > 0: the thread also backs off between tries, for
+// waits that are long and off the critical path (a polling warp otherwise takes issue slots from the warps that work).  The
+// clock is read only every 256 tries.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, uint32_t sleep_ns = 0) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();

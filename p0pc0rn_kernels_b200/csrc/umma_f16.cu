@@ -4,7 +4,7 @@
 namespace p0p {
 
 umma_kernel_fn umma_kernel_f16(uint32_t epi) {
-  static const umma_kernel_fn table[7] = P0P_UMMA_TABLE(P0P_ENC_F16);
+  static const umma_kernel_fn table[7] = P0P_UMMA_ROW(P0P_ENC_F16, 1, true);
   return table[epi];
 }
 

@@ -168,10 +168,19 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   const uint32_t acc_cols = atm ? 192u : 256u;
   u.KSPLIT = BT * 4u <= acc_cols ? 4u : BT * 2u <= acc_cols ? 2u : 1u;
   if (atm && u.KSPLIT == 1u && BT <= acc_cols && KSn >= 24u) { u.KSPLIT = 2u; u.NACC = 1u; }      // (depends on K and the tile only: conv3 chunks and the whole clip agree)
-  u.NS = (BT > 256u || (!atm && BT > 192u)) ? 3u : 4u;
+  // pipeline step: 128 k for quantised weights up to 256 tokens (the hand-over costs dominate there), 64 k otherwise (wide tiles
+  // are bound by the multiplies and their stages are large; fp16 weights are bound by shared memory).  Depends on the tile only.
+  u.KW = (atm && BT <= 256u) ? 2u : 1u;
+  // Token-ring stages: what shared memory allows for wide tiles; more for narrow ones, whose loads would otherwise be exposed.
+  // Operand stages: tensor memory holds four 32-column sub-stages.  Tiles above 128 tokens (bound by the multiplies): both rings
+  // in lock step on shared barriers.  fp16 weights have no operand ring of their own: the weight tile travels with the tokens.
+  if (!atm) { u.NS = BT > 192u ? 3u : 4u; u.NA = u.NS; u.LOCK = 1u; }
+  else if (BT > 256u) { u.NS = 3u; u.NA = 3u; u.LOCK = 1u; }
+  else if (BT > 128u) { u.NS = 2u; u.NA = 2u; u.LOCK = 1u; }
+  else { u.NS = BT > 64u ? 4u : BT > 32u ? 6u : 8u; u.NA = 2u; u.LOCK = 0u; }
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
-  const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + (size_t)U_EPI_BYTES + 512u;
+  const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * u.KW * BT * 128u + (size_t)U_EPI_BYTES + 1024u;
   u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (100 * 1024 + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
   if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
   u.m_tiles = (p.M + BT - 1u) / BT;
@@ -241,15 +250,16 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   } else mw = mx;
   const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
-  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 512u);
+  const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * u.KW * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 1024u);
   const int grid = (int)std::min<uint64_t>((uint64_t)u.T0 + (uint64_t)(tiles_all - u.T0) * u.S, sms);
   const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
-  const umma_kernel_fn kern = p.enc == P0P_ENC_Q4 ? umma_kernel_q4(p.epi) : p.enc == P0P_ENC_Q8 ? umma_kernel_q8(p.epi) : umma_kernel_f16(p.epi);
+  const uint32_t variant = u.KW == 1u ? 0u : u.LOCK ? 1u : 2u;
+  const umma_kernel_fn kern = p.enc == P0P_ENC_Q4 ? umma_kernel_q4(variant, p.epi) : p.enc == P0P_ENC_Q8 ? umma_kernel_q8(variant, p.epi) : umma_kernel_f16(p.epi);
   // the shared-memory ceiling is an attribute of (kernel, device): raised once for each pair
-  static DeviceOnce once[3][7];
+  static DeviceOnce once[3][3][7];
   cudaError_t e = cudaSuccess;
-  if (once[p.enc][p.epi].run(c->device, [&] { e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max); return (int)e; }))
+  if (once[p.enc][variant][p.epi].run(c->device, [&] { e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max); return (int)e; }))
     return cuda_fail(c, e != cudaSuccess ? e : cudaErrorInvalidDevice, "tensor-core kernel attribute");
   void* args[3] = {&u, &mx, &mw};
   if ((e = cudaLaunchKernel(reinterpret_cast<const void*>(kern), dim3(grid), dim3(U_THREADS), args, smem, c->stream)) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");

@@ -3,9 +3,9 @@
 
 namespace p0p {
 
-umma_kernel_fn umma_kernel_q4(uint32_t epi) {
-  static const umma_kernel_fn table[7] = P0P_UMMA_TABLE(P0P_ENC_Q4);
-  return table[epi];
+umma_kernel_fn umma_kernel_q4(uint32_t variant, uint32_t epi) {
+  static const umma_kernel_fn table[3][7] = {P0P_UMMA_ROW(P0P_ENC_Q4, 1, true), P0P_UMMA_ROW(P0P_ENC_Q4, 2, true), P0P_UMMA_ROW(P0P_ENC_Q4, 2, false)};
+  return table[variant][epi];
 }
 
 }  // namespace p0p

@@ -296,8 +296,8 @@ CONV_TC = [
          conv=dict(kind="conv", Hi=12, Wi=40, Ci=64, Ho=12, Wo=40, stride=1, padT=2, padL=2, ks=5)),
     dict(name="tc conv3x3 gn c64 f16", enc="f16", M=16 * 16, N=64, K=9 * 64, x_elems=16 * 16 * 64, w_scale=0.03, epi="bias",
          conv=dict(kind="conv", Hi=16, Wi=16, Ci=64, Ho=16, Wo=16, stride=1, padT=1, padL=1, ks=3, gn=True)),
-    dict(name="tc conv3x3 stride2 unpadded c128 f16", enc="f16", M=7 * 8, N=128, K=9 * 128, x_elems=15 * 17 * 128, w_scale=0.03,
-         conv=dict(kind="conv", Hi=15, Wi=17, Ci=128, Ho=7, Wo=8, stride=2, padT=0, padL=0, ks=3)),
+    dict(name="tc conv3x3 stride2 unpadded c128 f16", enc="f16", M=8 * 8, N=128, K=9 * 128, x_elems=17 * 17 * 128, w_scale=0.03,
+         conv=dict(kind="conv", Hi=17, Wi=17, Ci=128, Ho=8, Wo=8, stride=2, padT=0, padL=0, ks=3)),
     dict(name="tc conv3x3 c64 q4 320 tokens per tile", enc="q4", M=32 * 40, N=256, K=9 * 64, x_elems=32 * 40 * 64, epi="bias", res=True,
          conv=dict(kind="conv", Hi=32, Wi=40, Ci=64, Ho=32, Wo=40, stride=1, padT=1, padL=1, ks=3)),
 ]
@@ -378,8 +378,8 @@ def test_tensor_core_matches_general_kernel_bits_of_weights(gpu, oracle):
     weights equal f16(deq) bit for bit (fp32 accumulation of one non-zero product per output is exact)"""
     O = oracle
     K, N = 256, 256
-    for enc in ("q4g32a.t64", "q8g64s.t64"):
-        W0 = O.randn(N * K, 11, 0.05); Wb, deq = CS.encode(enc, W0, N, K)
+    for enc, scale in (("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q8g64s.t64", 1.0)):      # packed conversions and their fallbacks
+        W0 = O.randn(N * K, 11, scale); Wb, deq = CS.encode(enc, W0, N, K)
         X = np.eye(K, dtype=np.float32)
         wb, xb, yb = gpu.upload(Wb), gpu.upload(P().toF16(X)), gpu.buffer(K * N * 2)
         try:
@@ -466,7 +466,10 @@ def test_peer_copies_refused_on_general_kernel(gpu):
         CS.run_gpu(gpu, h)
 
 
-@pytest.mark.parametrize("enc,scale", [("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q4g32a.t64", "offset"), ("f16", 0.05)])
+# scales on both sides of the packed conversions' conditions (q4: scale < 2^-4 and the exactness window; q8: scale < 2^-8), down to
+# subnormal scales and minima
+@pytest.mark.parametrize("enc,scale", [("q4g32a.t64", 0.05), ("q8g64s.t64", 0.05), ("q4g32a.t64", 1.0), ("q4g32a.t64", "offset"), ("f16", 0.05),
+                                       ("q4g32a.t64", 0.02), ("q4g32a.t64", 2e-5), ("q4g32a.t64", 0.3), ("q8g64s.t64", 1.0), ("q8g64s.t64", 0.02), ("q8g64s.t64", 1e-4)])
 @pytest.mark.parametrize("path", [0, 1])
 def test_dequant_bit_exact(gpu, oracle, enc, scale, path):
     """every tile value the kernels multiply with equals f16(deq) of the encoder, bit for bit (docs/FORMAT.md)"""
