@@ -313,8 +313,28 @@ def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
             ms_c = graph_time(chunks, reps)
             torch.cuda.synchronize()
             same = bool(torch.equal(ya_t.view(torch.int16), yb_t.view(torch.int16)))
+            if world > 1:
+                # N = 128 output channels do not split along N: the ranks split the OUTPUT FRAMES (one-frame halo through padT / padL),
+                # every rank holding the clip; each rank's frames must hold the bits of the whole-clip call
+                import torch.distributed as dist
+                yc_t = torch.zeros(T * fy, device=dev, dtype=torch.float16); yc = gpu.wrap(yc_t.data_ptr(), T * fy * 2)
+                wa = {"w": {"enc": "f16", "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": K}, "x": {"buf": clip, "off": 0}, "y": {"buf": yc, "off": 0},
+                      "M": T * Hh * Ww, "N": N, "K": K, "epi": "bias", "ev": {"buf": bias},
+                      "conv": {"kind": "conv3", "Hi": Hh, "Wi": Ww, "Ci": C, "Ho": Hh, "Wo": Ww, "stride": T, "padT": 0, "padL": 0, "ks": 1}}
+                mine = P.conv3_frame_shard(wa, rank, world); t0f, nff = P.shard_frames(T, rank, world)
+                def shard():
+                    if mine is not None: P.gemm(gpu, mine)
+                ms_s = graph_time(shard, reps) if mine is not None else 0.0
+                tt = torch.tensor([ms_s], device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); ms_s = float(tt.item())
+                ok = torch.tensor([1 if torch.equal(yc_t[t0f * fy:(t0f + nff) * fy].view(torch.int16), ya_t[t0f * fy:(t0f + nff) * fy].view(torch.int16)) else 0], device=dev)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if rank == 0:
+                    fl_ = 2.0 * T * Hh * Ww * N * K
+                    print(json.dumps({"config": "conv3 (configs[3]) split by output frames", "n_gpus": world, "frames_per_rank": [P.shard_frames(T, r, world)[1] for r in range(world)],
+                                      "ms": ms_s, "TFLOP/s": fl_ / (ms_s * 1e-3) / 1e12, "speedup_vs_one_gpu_whole_clip": ms_w / ms_s,
+                                      "frame_shards_bit_identical_to_whole": bool(ok.item())}), flush=True)
             fl = 2.0 * T * Hh * Ww * N * K; by = T * fx * 2 + N * K * 2 + T * fy * 2 + N * 4
-            print(json.dumps({"config": "conv3 (configs[3])", "family": fam, "M": T * Hh * Ww, "N": N, "K": K, "ms_whole": ms_w, "ms_chunks_of_4_from_ring_of_6": ms_c,
+            if rank == 0: print(json.dumps({"config": "conv3 (configs[3])", "family": fam, "M": T * Hh * Ww, "N": N, "K": K, "ms_whole": ms_w, "ms_chunks_of_4_from_ring_of_6": ms_c,
                               "TFLOP/s_whole": fl / (ms_w * 1e-3) / 1e12, "TFLOP/s_chunks": fl / (ms_c * 1e-3) / 1e12, "GB/s_whole": by / (ms_w * 1e-3) / 1e9,
                               "frac_tensor_whole": fl / (ms_w * 1e-3) / 1e12 / pk["tensor"], "chunks_bit_identical_to_whole": same}), flush=True)
     torch.cuda.synchronize()

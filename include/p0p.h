@@ -43,7 +43,9 @@ enum {                                                                       /* 
   P0P_F_ROPE_HALF = 256  /* heads: ropeMode 'half' (pairs d, d+64)    */
 };
 /* which kernel family served the last p0p_gemm call (p0p_last_kernel) or is forced (p0p_gemm_args.force_kernel) */
-enum { P0P_K_AUTO = 0, P0P_K_GENERIC = 1, P0P_K_DECODE = 2, P0P_K_UMMA = 3 };
+enum { P0P_K_AUTO = 0, P0P_K_GENERIC = 1, P0P_K_DECODE = 2, P0P_K_UMMA = 3,
+       /* p0p_attention: the warp-level kernel / the tensor-memory kernel (p0p_attn_args.kernel forces one of them) */
+       P0P_K_ATTN_WARP = 16, P0P_K_ATTN_TMEM = 17 };
 
 enum { P0P_OPT_USE_STREAM = 1 };
 
@@ -191,13 +193,17 @@ int p0p_peer_barrier(p0p_ctx* ctx, p0p_buf* flags, p0p_buf* const* peer_flags, u
 /* attention, head_dim 128 (src/ops/attention.js:168-193; argument object types/index.d.ts `AttentionArgs`): the step after the
  * 'heads' projection.  Q [Hq][Lq][128] f16, K / V [Hkv][Lk][128] f16 head-major, O [Lq][ldo] f16 token-major at column h*128.
  * mode 0 none, 1 causal + valid length (key j visible to query i iff j <= min(i, nvalid-1)), 2 valid length (j < nvalid);
- * Hkv 0 = Hq, Lk 0 = Lq, ldo 0 = Hq*128, scale 0 = 1/sqrt(128), nvalid 0 = Lk.  *flops = 4*Lq*Lk*128*Hq (:192). */
+ * Hkv 0 = Hq, Lk 0 = Lq, ldo 0 = Hq*128, scale 0 = 1/sqrt(128), nvalid 0 = Lk.  *flops = 4*Lq*Lk*128*Hq (:192).
+ * Calls with at least 128 queries per head run on the tensor-memory kernel (tcgen05), which first writes a transposed copy
+ * of V into the context's scratch memory (sized on the first such call: not while recording a graph). */
 typedef struct p0p_attn_args {
   uint32_t struct_size;
   uint32_t Hq, Hkv, Lq, Lk, ldo, mode, nvalid;
   float scale;
   p0p_buf *q, *k, *v, *o;
   uint64_t q_off, k_off, v_off, o_off;   /* bytes */
+  uint32_t kernel;                       /* 0 = the library chooses; P0P_K_ATTN_WARP / P0P_K_ATTN_TMEM force one (tests).  A caller
+                                            built before this field existed passes a smaller struct_size and gets 0. */
 } p0p_attn_args;
 int p0p_attention(p0p_ctx* ctx, const p0p_attn_args* args, double* flops);
 

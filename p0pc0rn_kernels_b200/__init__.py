@@ -9,7 +9,8 @@ from .encode import (MANIFEST_FORMAT, chooseEncoding, dtypeBytes, encodeRows, ma
 from .gemm import DEFAULT_TILE, gemm
 from .gpu import MB, Buffer, Gpu, GpuError, createGpu, f2h, fromF16, h2f, toF16, view
 from .misc import gnFinalize, gnPartBytes, gnPartial, groupnormStats, pixstats, rowstats
-from .shard import all_gather_columns, shard_bytes, shard_rows, shard_swiglu_bytes, shard_weight
+from .shard import (all_gather_columns, all_gather_frames, conv3_frame_shard, shard_bytes, shard_frames, shard_rows, shard_swiglu_bytes,
+                    shard_weight)
 from .tune import TUNE_TABLE, calibrate, defaultTune, tuneEntry
 from .weights import loadWeights, uploadWeights
 

@@ -47,7 +47,7 @@ class GemmArgs(C.Structure):
 
 class AttnArgs(C.Structure):
     _fields_ = ([(n, C.c_uint32) for n in ("struct_size", "Hq", "Hkv", "Lq", "Lk", "ldo", "mode", "nvalid")] + [("scale", C.c_float)]
-                + [(n, C.c_void_p) for n in ("q", "k", "v", "o")] + [(n, C.c_uint64) for n in ("q_off", "k_off", "v_off", "o_off")])
+                + [(n, C.c_void_p) for n in ("q", "k", "v", "o")] + [(n, C.c_uint64) for n in ("q_off", "k_off", "v_off", "o_off")] + [("kernel", C.c_uint32)])
 
 
 def _load():

@@ -40,6 +40,7 @@ bool decode_supported(const KP& p) {
 uint64_t plan_decode(DecodeP& d, DecodeLaunch& L, int sms, size_t smem_per_sm) {
   const KP& p = d.p;
   d.Mp = p.M <= 8u ? 8u : 16u;
+  d.vec32 = (p.xmode != P0P_X_F16 && (((uintptr_t)p.X | (uintptr_t)(p.PV + p.pvOff)) & 15u) == 0u && p.ldx % 4u == 0u && p.kx0 % 4u == 0u && (p.xmode != P0P_X_LNMOD || p.pvStride % 4u == 0u)) ? 1u : 0u;
   const uint32_t cols = p.epi == P0P_EPI_SWIGLU ? p.N / 2u : ((p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u * 128u : p.N);
   d.th = (cols + 63u) / 64u;
   // tiles past the weight's last row do not exist: columns there read the last tile (their outputs are never stored)

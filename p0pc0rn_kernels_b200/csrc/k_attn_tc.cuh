@@ -1,0 +1,251 @@
+// Flash attention, head_dim 128, on the 5th-generation tensor cores (src/ops/attention.js): the same contract as
+// k_attn.cuh (Q [Hq][Lq][128], K [Hkv][Lk][128] f16 head-major; O [Lq][ldo] token-major; mask modes 0 / 1 / 2; GQA), with
+// V given TRANSPOSED, [Hkv][128][ldv] (a pre-pass makes that copy), so that both products take K-major operands:
+//   S = Q K^T   A = Q tile [128 q][128 d] (shared memory),  B = K tile [128 keys][128 d] (shared memory)
+//   O += P V    A = P tile [128 q][128 keys] (tensor memory), B = V^T tile [128 d][128 keys] (shared memory)
+// One block = two tiles of 128 queries of one head that share every K / V tile.  Tensor memory (512 columns x 128 lanes):
+// S of tile A | S of tile B | O of tile A | O of tile B, 128 fp32 columns each; lane = query row.  P (fp16, two keys per
+// column) is written over the first 64 columns of its S, which is free once the softmax threads hold the row.
+// Roles: warp 0 loads tiles by tensor-map copies into a ring of 32-KB slots (K0 V0 K1 V1 ...); warp 1 issues the
+// multiplies in the order  PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1), so that while the softmax of one tile runs the tensor
+// cores work on the other; warps 2-5 are the softmax of tile A, warps 6-9 of tile B: one thread per query row, the whole
+// row of 128 scores in registers (no shuffles).  The running maximum is only raised when it grew by more than 2^8: until
+// then P is at most 256 (fine in fp16) and O needs no rescaling, which is a pass over tensor memory.  "S(j+1) ready"
+// implies "PV(j) done" (a commit covers every earlier multiply), so the softmax threads may rescale O when they hold S.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "sync.cuh"
+#include "umma.cuh"
+
+namespace p0p {
+
+struct AttnTcP {
+  __half* O;
+  uint32_t Lq, Lk, ldo, Hq, Hkv, mode, nvalid;
+  float scale_log2;      // scale * log2(e)
+  int* status;           // bounded waits report here
+};
+
+constexpr uint32_t ATC_THREADS = 320u, ATC_TILE = 32768u, ATC_SLOTS = 4u;
+constexpr uint32_t ATC_SMEM = 1024u + (2u + ATC_SLOTS) * ATC_TILE + 256u;      // alignment slack + Q tiles + ring + barriers
+
+__device__ __forceinline__ float atc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+__global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                                                            const __grid_constant__ CUtensorMap mapV) {
+  extern __shared__ unsigned char atc_raw[];
+  const uint32_t base = (smem_u32(atc_raw) + 1023u) & ~1023u;
+  unsigned char* gbase = atc_raw + (base - smem_u32(atc_raw));
+  const uint32_t q_sm = base, kv_sm = base + 2u * ATC_TILE, bars = kv_sm + ATC_SLOTS * ATC_TILE;
+  const uint32_t q_full = bars, kv_full = bars + 8u, kv_empty = kv_full + 8u * ATC_SLOTS, s_full = kv_empty + 8u * ATC_SLOTS;
+  const uint32_t p_full = s_full + 16u, o_full = p_full + 16u, tmem_slot = o_full + 16u;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const uint32_t h = blockIdx.y, hk = h / (p.Hq / p.Hkv), q0 = blockIdx.x * 256u;
+  const bool hasB = q0 + 128u < p.Lq;
+  // keys any row of this block can see, and the key tiles that covers                        (attention.js:64)
+  uint32_t kEnd = p.Lk;
+  if (p.mode == 1u) kEnd = min(p.Lk, min(q0 + 255u, p.nvalid - 1u) + 1u);
+  if (p.mode == 2u) kEnd = min(p.Lk, p.nvalid);
+  const uint32_t nj = (kEnd + 127u) >> 7;
+
+  if (tid == 0) {
+    mbar_init(q_full, 1u);
+    for (uint32_t s = 0; s < ATC_SLOTS; s++) { mbar_init(kv_full + 8u * s, 1u); mbar_init(kv_empty + 8u * s, 1u); }
+    for (uint32_t t = 0; t < 2u; t++) { mbar_init(s_full + 8u * t, 1u); mbar_init(p_full + 8u * t, 4u); mbar_init(o_full + 8u * t, 1u); }
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512u); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(gbase + (tmem_slot - base));
+
+  if (warp == 0) {
+    // ================================================================= loads
+    if (lane == 0) {
+      mbar_expect_tx(q_full, hasB ? 2u * ATC_TILE : ATC_TILE);
+      for (uint32_t t = 0; t < (hasB ? 2u : 1u); t++)
+        for (uint32_t c = 0; c < 2u; c++) tma_load_3d(q_sm + t * ATC_TILE + c * 16384u, &mapQ, (int)(c * 64u), (int)(q0 + t * 128u), (int)h, q_full);
+      for (uint32_t i = 0; i < 2u * nj; i++) {
+        const uint32_t slot = i % ATC_SLOTS, use = i / ATC_SLOTS, j = i >> 1, dst = kv_sm + slot * ATC_TILE, bar = kv_full + 8u * slot;
+        if (use > 0u && !mbar_wait(kv_empty + 8u * slot, (use - 1u) & 1u, p.status, 401, 100u)) break;
+        mbar_expect_tx(bar, ATC_TILE);
+        if (i & 1u) { for (uint32_t c = 0; c < 2u; c++) tma_load_3d(dst + c * 16384u, &mapV, (int)(j * 128u + c * 64u), 0, (int)hk, bar); }
+        else { for (uint32_t c = 0; c < 2u; c++) tma_load_3d(dst + c * 16384u, &mapK, (int)(c * 64u), (int)(j * 128u), (int)hk, bar); }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================= multiplies (the whole warp walks the loop, one lane issues)
+    const uint32_t idesc = umma_idesc_f16(128u, 128u), nt = hasB ? 2u : 1u;
+    const uint64_t qd[2] = {umma_desc_sw128(q_sm), umma_desc_sw128(q_sm + ATC_TILE)};
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0u, p.status, 402) && mbar_wait(kv_full, 0u, p.status, 403));
+    if (ok) {
+      tc_fence_after();
+      const uint64_t kd = umma_desc_sw128(kv_sm);
+      if (elect_one()) {
+        for (uint32_t t = 0; t < nt; t++) {
+#pragma unroll
+          for (uint32_t kk = 0; kk < 8u; kk++) umma_f16_ss(tmem_base + t * 128u, qd[t] + (kk >> 2) * 1024u + 2u * (kk & 3u), kd + (kk >> 2) * 1024u + 2u * (kk & 3u), idesc, kk);
+          umma_commit(s_full + 8u * t);
+        }
+        umma_commit(kv_empty);
+      }
+      __syncwarp();
+    }
+    for (uint32_t j = 0; j < nj && ok; j++) {
+      const uint32_t iv = 2u * j + 1u, sv = iv % ATC_SLOTS, ik = iv + 1u, sk = ik % ATC_SLOTS;
+      const bool more = j + 1u < nj;
+      bool rdy = mbar_wait(kv_full + 8u * sv, (iv / ATC_SLOTS) & 1u, p.status, 404);
+      if (more) rdy = rdy && mbar_wait(kv_full + 8u * sk, (ik / ATC_SLOTS) & 1u, p.status, 405);
+      if (!__all_sync(0xffffffffu, rdy)) { ok = false; break; }
+      const uint64_t vd = umma_desc_sw128(kv_sm + sv * ATC_TILE), kd = umma_desc_sw128(kv_sm + sk * ATC_TILE);
+      for (uint32_t t = 0; t < nt; t++) {
+        if (!__all_sync(0xffffffffu, mbar_wait(p_full + 8u * t, j & 1u, p.status, 406))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t s_col = tmem_base + t * 128u, o_col = tmem_base + 256u + t * 128u;
+        const uint64_t qdt = qd[t];
+        if (elect_one()) {
+#pragma unroll
+          for (uint32_t kk = 0; kk < 8u; kk++) umma_f16_ts(o_col, s_col + 8u * kk, vd + (kk >> 2) * 1024u + 2u * (kk & 3u), idesc, j | kk);
+          if (more) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 8u; kk++) umma_f16_ss(s_col, qdt + (kk >> 2) * 1024u + 2u * (kk & 3u), kd + (kk >> 2) * 1024u + 2u * (kk & 3u), idesc, kk);
+            umma_commit(s_full + 8u * t);
+          } else
+            umma_commit(o_full + 8u * t);
+        }
+        __syncwarp();
+      }
+      if (ok && elect_one()) {
+        umma_commit(kv_empty + 8u * sv);
+        if (more) umma_commit(kv_empty + 8u * sk);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ================================================================= softmax of one tile: thread = query row
+    const uint32_t t = (warp - 2u) >> 2, qd = warp & 3u, row = qd * 32u + lane, i = q0 + t * 128u + row;
+    if (t == 0u || hasB) {
+      const uint32_t lane_addr = tmem_base + ((qd * 32u) << 16), s_addr = lane_addr + t * 128u, o_addr = lane_addr + 256u + t * 128u;
+      uint32_t limit = p.Lk;                                                                  // keys [0, limit) are visible to this row
+      if (p.mode == 1u) limit = min(p.Lk, min(i, p.nvalid - 1u) + 1u);
+      if (p.mode == 2u) limit = min(p.Lk, p.nvalid);
+      const float sc = p.scale_log2;
+      float m_used = -INFINITY, l = 0.0f;
+      bool ok = true;
+      for (uint32_t j = 0; j < nj; j++) {
+        if (!mbar_wait(s_full + 8u * t, j & 1u, p.status, 407)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[128];
+#pragma unroll
+        for (int c = 0; c < 8; c++) tmem_ld16(s_addr + 16u * c, *reinterpret_cast<uint32_t(*)[16]>(&s[16 * c]));
+        tmem_ld_wait();
+        const int rel = (int)limit - (int)(j * 128u);                                         // columns [0, rel) of this tile are visible
+        if (__any_sync(0xffffffffu, rel < 128)) {
+#pragma unroll
+          for (int c = 0; c < 128; c++) s[c] = c < rel ? s[c] : 0xff800000u;
+        }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 128; c += 4) {
+          mx[0] = fmaxf(mx[0], __uint_as_float(s[c])); mx[1] = fmaxf(mx[1], __uint_as_float(s[c + 1]));
+          mx[2] = fmaxf(mx[2], __uint_as_float(s[c + 2])); mx[3] = fmaxf(mx[3], __uint_as_float(s[c + 3]));
+        }
+        const float mts = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;
+        if (__any_sync(0xffffffffu, mts > m_used + 8.0f)) {
+          // raise the reference maximum of the whole warp's rows; O and l are rescaled to it
+          const float m_new = fmaxf(m_used, mts);
+          const float alpha = m_new == -INFINITY ? 1.0f : atc_ex2(m_used - m_new);
+          l *= alpha;
+          if (j > 0u) {
+#pragma unroll 1
+            for (uint32_t c = 0; c < 8u; c++) {
+              uint32_t o[16];
+              tmem_ld16(o_addr + 16u * c, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st16(o_addr + 16u * c, o);
+            }
+          }
+          m_used = m_new;
+        }
+        float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float nm = -m_used;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; e++) {
+            const float p0 = atc_ex2(fmaf(__uint_as_float(s[32 * c + 2 * e]), sc, nm)), p1 = atc_ex2(fmaf(__uint_as_float(s[32 * c + 2 * e + 1]), sc, nm));
+            ls[e & 3] += p0 + p1;
+            const __half2 hp = __floats2half2_rn(p0, p1);
+            pk[e] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+          tmem_st16(s_addr + 16u * c, pk);
+        }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + 8u * t);
+      }
+      // ---- O / l -> global, token-major, head h at column h * 128
+      if (ok && mbar_wait(o_full + 8u * t, 0u, p.status, 408)) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        __half* dst = p.O + (size_t)i * p.ldo + h * 128u;
+        const bool vec = ((reinterpret_cast<uintptr_t>(p.O) | ((uintptr_t)p.ldo * 2u)) & 15u) == 0u;
+#pragma unroll 1
+        for (uint32_t c = 0; c < 8u; c++) {
+          uint32_t o[16], w[8];
+          tmem_ld16(o_addr + 16u * c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const __half2 hp = __floats2half2_rn(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
+            w[e] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+          if (i < p.Lq) {
+            if (vec) {
+              *reinterpret_cast<uint4*>(dst + 16u * c) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(dst + 16u * c + 8u) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; e++) *reinterpret_cast<uint32_t*>(dst + 16u * c + 2 * e) = w[e];
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512u); }
+}
+
+// V [Hkv][Lk][128] -> V^T [Hkv][128][ldv] (ldv >= Lk, a multiple of 8): 64 keys x 128 dims per block through shared memory
+__global__ void __launch_bounds__(256) k_attn_vt(const __half* __restrict__ V, __half* __restrict__ Vt, uint32_t Lk, uint32_t ldv) {
+  __shared__ __half tile[64][130];
+  const uint32_t hk = blockIdx.y, k0 = blockIdx.x * 64u, tid = threadIdx.x;
+  const __half* src = V + (size_t)hk * Lk * 128u;
+  for (uint32_t e = tid; e < 64u * 64u; e += 256u) {             // 64 keys x 64 pairs of dims
+    const uint32_t r = e >> 6, c = e & 63u;
+    const uint32_t v = k0 + r < Lk ? __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)(k0 + r) * 128u) + c) : 0u;
+    *reinterpret_cast<uint32_t*>(&tile[r][2u * c]) = v;
+  }
+  __syncthreads();
+  __half* dst = Vt + (size_t)hk * 128u * ldv;
+  for (uint32_t e = tid; e < 128u * 32u; e += 256u) {            // 128 dims x 32 pairs of keys
+    const uint32_t d = e >> 5, kp = e & 31u, k = k0 + 2u * kp;
+    if (k < ldv) {                                                // ldv is even: the pair is inside the row
+      const __half2 o = __halves2half2(tile[2u * kp][d], tile[2u * kp + 1u][d]);
+      *reinterpret_cast<__half2*>(dst + (size_t)d * ldv + k) = o;
+    }
+  }
+}
+
+}  // namespace p0p

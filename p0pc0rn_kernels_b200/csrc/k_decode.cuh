@@ -5,12 +5,14 @@
 //            about three blocks per SM.  In each block one producer lane moves whole records from global to
 //            shared memory with bulk asynchronous copies (cp.async.bulk, mbarrier-tracked, a ring of stages);
 //            eight consumer warps: four row groups of 16 rows, two warps each that split a stage's records.
-//            Codes go to the tensor cores WITHOUT being dequantised: a 4-bit code q becomes the fp16 bit pattern 0x6400|q (= 1024+q) or 0x6400|q<<4
-//            (= 1024+16q) by one lop3, an 8-bit code the pattern 0x6400|(q+128), and mma.sync.m16n8k16
-//            (weights = A, tokens = B, fp32 accumulate) sums code*x over one group.  The group's scale and
-//            minimum are applied to the fp32 sum afterwards:  y += s * (acc - C) + mn * Sx,  where
-//            C (the sum of the pattern offsets times x) and Sx (the sum of x) depend only on the tokens and
-//            are tabulated once per k-block.  The tokens are staged in shared memory in the operand order
+//            Codes go to the tensor cores WITHOUT being dequantised.  A 4-bit code q is left where it sits and read as
+//            an fp16 SUBNORMAL: masked to bits 0..3 of a half it is q * 2^-24, masked to bits 4..7 it is 16 q * 2^-24
+//            (its token is staged pre-divided by 16), one AND per code pair and no offset to correct for.  An 8-bit
+//            code becomes the pattern 0x6400|(q+128) (= 1152 + q).  mma.sync.m16n8k16 (weights = A, tokens = B, fp32
+//            accumulate) sums code * x over one group; the group's scale and minimum are applied to the fp32 sum:
+//            q4:  y += (s * 2^24) * acc + mn * Sx;   q8:  y += s * (acc - 1152 * Sx),
+//            where Sx (the sum of the group's tokens) depends only on the tokens and is tabulated once per k-block
+//            (q8: as the accumulator's starting value).  The tokens are staged in shared memory in the operand order
 //            of the instruction, with the fused prologue (plain fp16 / RMSNorm / LayerNorm+modulation)
 //            applied on the way in.  Each unit's 64 x M partial sums go to a scratch buffer.
 //   stage 2  k_decode_finish   sums the k-block partials in a fixed order (deterministic, no atomics) and
@@ -47,6 +49,7 @@ struct DecodeP {
   uint32_t nslots;    // tiles * 64
   float* scratch;     // [S][M][nslots] fp32
   int* status;
+  uint32_t vec32;     // fp32 tokens and the prologue vector may be read with 16-byte loads
 };
 
 // weight tile index (64 rows) of unit-local tile t
@@ -55,74 +58,73 @@ __device__ __forceinline__ uint32_t d_tile_row0(const DecodeP& d, uint32_t t) {
   return d.p.wR0 + t * 64u;
 }
 
-// ---- token staging: one thread per (token, scale group: 32 k for q4, 64 k for q8).  Writes the group's tokens in
-// operand order and its correction terms.
-//   ctc[gi][token pair] = float4(-C_a, -C_b, -C_a, -C_b): the accumulator fragment (rows g / g+8 x tokens a, b) the
-//                         multiply starts from;  q4: C = 1024 * sum(x, even k) + 64 * sum(x, odd k),  q8: C = 1152 * sum(x)
-//   cts[gi][token pair] = float2(Sx_a, Sx_b), the plain sums (q4 only: they carry the group minimum)
+// ---- token staging: one thread per (token, 8 consecutive k): 16-byte loads, the fused prologue, 16 bytes of operand.
+// The 4 (q4: groups of 32 k) or 8 (q8: groups of 64 k) neighbouring lanes of a scale group add up the group's token sum:
+//   cts[gi][token pair] = float2(Sx_a, Sx_b)                     q4: the plain sums (they carry the group minimum)
+//   ctc[gi][token pair] = float4(-C_a, -C_b, -C_a, -C_b)          q8: C = 1152 * Sx, the accumulator fragment (rows g / g+8 x
+//                                                                tokens a, b) the multiply starts from
+// klen is a multiple of 256, so a warp's 32 items are consecutive chunks of ONE token and the lane groups line up.
 template <int ENC, int XMODE, int MP>
 __device__ __forceinline__ void d_stage_tokens(const DecodeP& d, uint32_t kb0, uint32_t klen, unsigned char* xs, float* ctc, float* cts, uint32_t tok_stride, uint32_t tid) {
   const KP& p = d.p;
-  constexpr uint32_t GS = ENC == P0P_ENC_Q4 ? 32u : 64u;
-  const uint32_t groups = klen / GS;
-  for (uint32_t it = tid; it < p.M * groups; it += D_CONSUMERS) {
-    const uint32_t m = it / groups, gi = it % groups, k0 = kb0 + gi * GS;
-    float sx = 0.0f, se = 0.0f;
+  constexpr uint32_t GL = ENC == P0P_ENC_Q4 ? 4u : 8u;            // lanes per scale group
+  const uint32_t chunks = klen / 8u, lane = tid & 31u;
+  for (uint32_t it = tid; it < p.M * chunks; it += D_CONSUMERS) {
+    const uint32_t m = it / chunks, c8 = it - m * chunks, k0 = kb0 + c8 * 8u;
+    float v[8];
+    if (XMODE == P0P_X_F16) {
+      const __half* src = reinterpret_cast<const __half*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
+      if (p.vecx) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(src));
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-    for (uint32_t part = 0; part < GS / 32u; part++) {
-      float v[32];
-      if (XMODE == P0P_X_F16) {
-        const __half* src = reinterpret_cast<const __half*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0 + part * 32u;
-        if (p.vecx) {
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + q);
-            const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-            for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); v[q * 8 + 2 * i] = f.x; v[q * 8 + 2 * i + 1] = f.y; }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) v[i] = __half2float(src[i]);
-        }
-      } else {
-        const float* src = reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0 + part * 32u;
-        const size_t sr = ((size_t)p.statOff + m) * 2u;
-        const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
-        const float* pv = p.PV + p.pvOff + p.kx0 + k0 + part * 32u;
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const float xv = __ldg(src + i);
-          const float t = XMODE == P0P_X_LNMOD ? (xv - mean) * rstd * (1.0f + __ldg(pv + i)) + __ldg(pv + p.pvStride + i) : xv * rstd * __ldg(pv + i);
-          v[i] = __half2float(__float2half_rn(t));          // the prologue's result is an fp16 value (src/ops/gemm.js:66-67)
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 32; i++) { sx += v[i]; if (!(i & 1)) se += v[i]; }
-      __half2 o[16];
-      if (ENC == P0P_ENC_Q4) {
-        // per 8 columns: [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16]  (odd nibbles carry 16*q, so their token is pre-divided)
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-          const float* w = v + 8 * b;
-          o[4 * b + 0] = __floats2half2_rn(w[0], w[4]);
-          o[4 * b + 1] = __floats2half2_rn(w[1] * 0.0625f, w[5] * 0.0625f);
-          o[4 * b + 2] = __floats2half2_rn(w[2], w[6]);
-          o[4 * b + 3] = __floats2half2_rn(w[3] * 0.0625f, w[7] * 0.0625f);
-        }
+        for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; i++) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        for (int i = 0; i < 8; i++) v[i] = __half2float(src[i]);
       }
-      uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * tok_stride + (k0 - kb0 + part * 32u) * 2u);
+    } else {
+      // (the host admits this kernel only when x rows and the vector are 16-byte aligned: see decode_supported)
+      const float* src = reinterpret_cast<const float*>(p.X) + (size_t)m * p.ldx + p.kx0 + k0;
+      const size_t sr = ((size_t)p.statOff + m) * 2u;
+      const float mean = __ldg(p.ST + sr), rstd = __ldg(p.ST + sr + 1);
+      const float* pv = p.PV + p.pvOff + p.kx0 + k0;
+      float xv[8], g1[8], g2[8];
+      if (d.vec32) {
+        *reinterpret_cast<float4*>(xv) = __ldg(reinterpret_cast<const float4*>(src)); *reinterpret_cast<float4*>(xv + 4) = __ldg(reinterpret_cast<const float4*>(src) + 1);
+        *reinterpret_cast<float4*>(g1) = __ldg(reinterpret_cast<const float4*>(pv)); *reinterpret_cast<float4*>(g1 + 4) = __ldg(reinterpret_cast<const float4*>(pv) + 1);
+        if (XMODE == P0P_X_LNMOD) { *reinterpret_cast<float4*>(g2) = __ldg(reinterpret_cast<const float4*>(pv + p.pvStride)); *reinterpret_cast<float4*>(g2 + 4) = __ldg(reinterpret_cast<const float4*>(pv + p.pvStride) + 1); }
+      } else {
 #pragma unroll
-      for (int q = 0; q < 4; q++) dst[q] = reinterpret_cast<const uint4*>(o)[q];
+        for (int i = 0; i < 8; i++) { xv[i] = __ldg(src + i); g1[i] = __ldg(pv + i); if (XMODE == P0P_X_LNMOD) g2[i] = __ldg(pv + p.pvStride + i); }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float t = XMODE == P0P_X_LNMOD ? (xv[i] - mean) * rstd * (1.0f + g1[i]) + g2[i] : xv[i] * rstd * g1[i];
+        v[i] = __half2float(__float2half_rn(t));            // the prologue's result is an fp16 value (src/ops/gemm.js:66-67)
+      }
     }
-    // q4: even nibbles enter the multiply as 1024 + q, odd ones as (1024 + 16 q) / 16 = 64 + q;  q8: codes enter as 1024 + 128 + q
-    const float negc = ENC == P0P_ENC_Q4 ? -(1024.0f * se + 64.0f * (sx - se)) : -1152.0f * sx;
-    float* c = ctc + ((size_t)gi * (MP / 2) + (m >> 1)) * 4u + (m & 1u);
-    c[0] = negc; c[2] = negc;
-    if (ENC == P0P_ENC_Q4) cts[((size_t)gi * (MP / 2) + (m >> 1)) * 2u + (m & 1u)] = sx;
+    float sx = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    __half2 o[4];
+    if (ENC == P0P_ENC_Q4) {
+      // per 8 columns: [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16]  (odd nibbles carry 16*q, so their token is pre-divided)
+      o[0] = __floats2half2_rn(v[0], v[4]);
+      o[1] = __floats2half2_rn(v[1] * 0.0625f, v[5] * 0.0625f);
+      o[2] = __floats2half2_rn(v[2], v[6]);
+      o[3] = __floats2half2_rn(v[3] * 0.0625f, v[7] * 0.0625f);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(xs + (size_t)m * tok_stride + (size_t)c8 * 16u) = *reinterpret_cast<const uint4*>(o);
+    // the group's sum: its GL lanes are neighbours (a whole warp always runs this loop body together: M * chunks is a multiple of 32)
+#pragma unroll
+    for (uint32_t o2 = 1; o2 < GL; o2 <<= 1) sx += __shfl_xor_sync(0xffffffffu, sx, o2);
+    if ((lane & (GL - 1u)) == 0u) {
+      const uint32_t gi = c8 / GL;
+      if (ENC == P0P_ENC_Q4) cts[((size_t)gi * (MP / 2) + (m >> 1)) * 2u + (m & 1u)] = sx;
+      else { float* c = ctc + ((size_t)gi * (MP / 2) + (m >> 1)) * 4u + (m & 1u); c[0] = -1152.0f * sx; c[2] = -1152.0f * sx; }
+    }
   }
 }
 
@@ -162,30 +164,30 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // per-lane constants of the consumer loop
 struct DLane { uint32_t MLO, MHI, MAGIC; uint32_t on0, on1; bool one; };
 
-// one q4 record (64 rows x 32 k) of this warp's share of a stage: R is its index in the share
+// one q4 record (64 rows x 32 k) of this warp's share of a stage: R is its index in the share.  ta: sums of s * acc (to be
+// scaled by 2^24), tb: sums of mn * Sx.
 template <int MP, uint32_t R>
-__device__ __forceinline__ void d_rec_q4(float (&tot)[MP / 8][4], uint32_t ca, uint32_t sa, uint32_t xk0, uint32_t xk1, uint32_t ck, uint32_t sk, const DLane& L) {
+__device__ __forceinline__ void d_rec_q4(float (&ta)[MP / 8][4], float (&tb)[MP / 8][4], uint32_t ca, uint32_t sa, uint32_t xk0, uint32_t xk1, uint32_t sk, const DLane& L) {
   const uint32_t wl = lds32<R * 1280u>(ca), wh = lds32<R * 1280u + 128u>(ca);
   const uint32_t sml = lds32<R * 1280u>(sa), smh = lds32<R * 1280u + 32u>(sa);
-  // nibble pairs as fp16 patterns: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
+  // nibble pairs as fp16 subnormals: (k0,k4) (k1,k5) of the low byte pair, then (k2,k6) (k3,k7)
   const uint32_t wl8 = wl >> 8, wh8 = wh >> 8;
-  const uint32_t l0 = and_or(wl, L.MLO, L.MAGIC), h0 = and_or(wl, L.MHI, L.MAGIC), l1 = and_or(wl8, L.MLO, L.MAGIC), h1 = and_or(wl8, L.MHI, L.MAGIC);
-  const uint32_t L0 = and_or(wh, L.MLO, L.MAGIC), H0 = and_or(wh, L.MHI, L.MAGIC), L1 = and_or(wh8, L.MLO, L.MAGIC), H1 = and_or(wh8, L.MHI, L.MAGIC);
+  const uint32_t l0 = wl & L.MLO, h0 = wl & L.MHI, l1 = wl8 & L.MLO, h1 = wl8 & L.MHI;
+  const uint32_t L0 = wh & L.MLO, H0 = wh & L.MHI, L1 = wh8 & L.MLO, H1 = wh8 & L.MHI;
   const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&sml)), fh = __half22float2(*reinterpret_cast<const __half2*>(&smh));   // (scale, min)
+  const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
   for (int h = 0; h < MP / 8; h++) {
-    const uint4 b = h == 0 ? lds128_if<R * 64u>(xk0, L.on0) : lds128_if<R * 64u>(xk1, L.on1);
-    const float4 c = h == 0 ? lds128f<R * (MP / 2) * 16u>(ck) : lds128f<(R * (MP / 2) + 4u) * 16u>(ck);      // the accumulator starts at -C
+    const uint4 b = h == 0 ? lds128<R * 64u>(xk0) : lds128<R * 64u>(xk1);                     // token columns past M read the row of zeros
     const float2 sx = h == 0 ? lds64f<R * (MP / 2) * 8u>(sk) : lds64f<(R * (MP / 2) + 4u) * 8u>(sk);
-    const float cin[4] = {c.x, c.y, c.z, c.w};
     float acc[4], acc2[4];
-    mma_16816(acc, l0, L0, h0, H0, b.x, b.y, cin);
+    mma_16816(acc, l0, L0, h0, H0, b.x, b.y, zero);
     mma_16816(acc2, l1, L1, h1, H1, b.z, b.w, acc);
-    tot[h][0] = fmaf(fl.y, sx.x, fmaf(fl.x, acc2[0], tot[h][0]));
-    tot[h][2] = fmaf(fh.y, sx.x, fmaf(fh.x, acc2[2], tot[h][2]));
+    ta[h][0] = fmaf(fl.x, acc2[0], ta[h][0]); tb[h][0] = fmaf(fl.y, sx.x, tb[h][0]);
+    ta[h][2] = fmaf(fh.x, acc2[2], ta[h][2]); tb[h][2] = fmaf(fh.y, sx.x, tb[h][2]);
     if (!L.one) {
-      tot[h][1] = fmaf(fl.y, sx.y, fmaf(fl.x, acc2[1], tot[h][1]));
-      tot[h][3] = fmaf(fh.y, sx.y, fmaf(fh.x, acc2[3], tot[h][3]));
+      ta[h][1] = fmaf(fl.x, acc2[1], ta[h][1]); tb[h][1] = fmaf(fl.y, sx.y, tb[h][1]);
+      ta[h][3] = fmaf(fh.x, acc2[3], ta[h][3]); tb[h][3] = fmaf(fh.y, sx.y, tb[h][3]);
     }
   }
 }
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   const uint32_t cts_l = smem_u32(cts) + (half * RPW * (MP / 2) + tp) * 8u;
   float* comb_l = comb + (rg * 32u + lane) * (MP / 2);
   DLane L;
-  L.MLO = 0x000f000fu; L.MHI = 0x00f000f0u; L.MAGIC = 0x64006400u;
+  L.MLO = 0x000f000fu; L.MHI = 0x00f000f0u; L.MAGIC = 0x64006400u;      // (masks live in registers: as immediates each AND would cost a constant load)
   L.on0 = g < p.M ? 1u : 0u; L.on1 = g + 8u < p.M ? 1u : 0u;            // does this lane's token column exist?
   L.one = p.M == 1u;                                                     // a single token: only the accumulators of token 0 are kept up
   uint32_t s = 0, ph = 0, cur_kb = 0xffffffffu;
@@ -306,26 +308,26 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
       bar_sync_named(1, D_CONSUMERS);
       cur_kb = kb;
     }
-    float tot[MP / 8][4];
+    float tot[MP / 8][4], tmn[MP / 8][4];            // q4: tot = sums of s * acc (still to be scaled by 2^24), tmn = sums of mn * Sx
 #pragma unroll
     for (int h = 0; h < MP / 8; h++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) tot[h][i] = 0.0f;
+      for (int i = 0; i < 4; i++) { tot[h][i] = 0.0f; tmn[h][i] = 0.0f; }
 
     for (uint32_t k = 0; ok && k < klen; k += D_STAGE_K) {
       if (!mbar_wait(full0 + 8u * s, ph, d.status, 102)) { ok = false; break; }
       const uint32_t so = anchor(s * D_STAGE_BYTES), ko = anchor(k);
       const uint32_t ca = code0 + so, sa = sm0 + so;
       const uint32_t xk0 = xrow0 + ko * 2u, xk1 = xrow1 + ko * 2u;
-      const uint32_t ck = ctc_l + (ko / GS) * (MP / 2) * 16u;
       if (ENC == P0P_ENC_Q4) {
         const uint32_t sk = cts_l + (ko / GS) * (MP / 2) * 8u;
         static_assert(D_STAGE_K == 256, "four q4 records / two q8 records per consumer warp and stage");
-        d_rec_q4<MP, 0>(tot, ca, sa, xk0, xk1, ck, sk, L);
-        d_rec_q4<MP, 1>(tot, ca, sa, xk0, xk1, ck, sk, L);
-        d_rec_q4<MP, 2>(tot, ca, sa, xk0, xk1, ck, sk, L);
-        d_rec_q4<MP, 3>(tot, ca, sa, xk0, xk1, ck, sk, L);
+        d_rec_q4<MP, 0>(tot, tmn, ca, sa, xk0, xk1, sk, L);
+        d_rec_q4<MP, 1>(tot, tmn, ca, sa, xk0, xk1, sk, L);
+        d_rec_q4<MP, 2>(tot, tmn, ca, sa, xk0, xk1, sk, L);
+        d_rec_q4<MP, 3>(tot, tmn, ca, sa, xk0, xk1, sk, L);
       } else {
+        const uint32_t ck = ctc_l + (ko / GS) * (MP / 2) * 16u;
         d_rec_q8<MP, 0>(tot, ca, sa, xk0, xk1, ck, L);
         d_rec_q8<MP, 1>(tot, ca, sa, xk0, xk1, ck, L);
       }
@@ -335,6 +337,12 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     }
     // ---- the two warps of a row group add up (through shared memory), then this unit's partial sums go to
     // scratch[kb][token][slot].  Both named barriers are met in drain mode too.
+    if (ENC == P0P_ENC_Q4) {
+#pragma unroll
+      for (int h = 0; h < MP / 8; h++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) tot[h][i] = fmaf(tot[h][i], 16777216.0f, tmn[h][i]);      // the codes entered as q * 2^-24
+    }
     if (half == 1u) {
 #pragma unroll
       for (int h = 0; h < MP / 8; h++) *reinterpret_cast<float4*>(comb_l + 4 * h) = make_float4(tot[h][0], tot[h][1], tot[h][2], tot[h][3]);

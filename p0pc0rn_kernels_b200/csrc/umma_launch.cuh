@@ -7,6 +7,7 @@
 #include <cmath>
 
 #include "k_umma.cuh"
+#include "tmap.h"
 
 namespace p0p {
 
@@ -43,20 +44,6 @@ __global__ void k_prologue_gn(const KP p, __half* __restrict__ out) {
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-typedef CUresult (*tmap_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-inline tmap_encode_fn tmap_encoder() {
-  static tmap_encode_fn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult qr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess) fn = (tmap_encode_fn)f;
-    (void)cudaGetLastError();
-  }
-  return fn;
-}
 // [rows][ld] fp16, box 64 (k) x box_rows, 128-byte swizzle, rows past the end read as zero
 inline bool make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems, uint32_t box_rows) {
   tmap_encode_fn f = tmap_encoder();
@@ -147,10 +134,10 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if (is_conv) { u.cvR = conv_tile_rows(p, atm); BT = u.cvR * p.Wo; }
   else if (p.M <= 256u) BT = std::max(16u, (p.M + 15u) & ~15u);
   else {
-    uint64_t best = ~0ull; BT = 0;
+    double best = 1e300; BT = 0;
     for (uint32_t cand = bt_max; cand >= 128u; cand -= 16u) {
       if (cand > 256u && cand % 32u) continue;
-      const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand), rounds = (t + sms - 1) / sms;
+      const uint64_t t = (uint64_t)u.n_tiles * ((p.M + cand - 1u) / cand);
       // measured: a k-step costs ~750 cycles up to 256 tokens (four dependent multiplies, or the dequantisation) and
       // ~2.5 cycles per token beyond; a single-accumulator tile exposes its epilogue, whose cost per token depends on the kind
       const uint64_t kstep = std::max<uint64_t>(5u * cand / 2u, atm ? 750u : 720u);
@@ -158,7 +145,11 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
       // (with two accumulators the epilogue hides behind the next tile's k loop unless it is the longer of the two; it runs
       // about half as fast there, sharing the issue slots with the dequantisation)
       const uint64_t per_tile = (atm && cand > 192u) ? (uint64_t)KSn * kstep + epi_tok * cand : std::max<uint64_t>((uint64_t)KSn * kstep, 2u * epi_tok * cand);
-      if (rounds * per_tile < best) { best = rounds * per_tile; BT = cand; }
+      // Rounds of tiles over the SMs.  Fewer tiles than SMs: split-K (below) spreads their k loops over all SMs, so what counts
+      // is the total work, not one round of it.  A last round that is not full is split as well, at some cost.
+      const double whole = (double)(t / sms), frac = (double)(t % sms) / (double)sms;
+      const double rounds = t < sms ? frac : whole + (frac > 0.0 ? std::min(1.0, frac + 0.1) : 0.0);
+      if (rounds * (double)per_tile < best) { best = rounds * (double)per_tile; BT = cand; }
     }
   }
   u.BT = BT; u.NACC = (BT > (atm ? 192u : 256u)) ? 1u : 2u;

@@ -7,6 +7,12 @@ reference itself is single-device; this module has no counterpart there.
 
 The only collective is the all-gather of the output, and only when the consumer needs the full row
 (``all_gather_columns``); it runs through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in CPU tests).
+
+The 3x3x3 convolution (``conv3``) has too few output channels to split along N (128 in the reference's models); it
+splits by OUTPUT FRAMES instead: a rank computes frames [t0, t0 + nf) of the clip and reads input frames t0 - 1 ..
+t0 + nf, the one-frame halo on each side being what the op's own chunk arguments (``padT`` / ``padL`` / ``x.off``,
+src/ops/gemm.js:72-76) express.  A rank's call is the chunked call of the reference's tests
+(test/kernels.test.js:123-131), so its frames hold the bits of the whole-clip call.
 """
 from __future__ import annotations
 
@@ -63,3 +69,53 @@ def all_gather_columns(y_local, group=None):
     if M == 1:
         return stage.reshape(1, world * n)
     return stage.view(world, M, n).permute(1, 0, 2).reshape(M, world * n)
+
+
+def shard_frames(T: int, rank: int, world: int) -> tuple:
+    """-> (t0, nf): the contiguous range of output frames of rank; the first T % world ranks take one frame more (nf may be 0)"""
+    if not 0 <= rank < world: raise ValueError(f"rank {rank} is not inside a world of {world}")
+    q, r = divmod(T, world)
+    return rank * q + min(rank, r), q + (1 if rank < r else 0)
+
+
+def conv3_frame_shard(a: dict, rank: int, world: int, local_input: bool = False) -> dict | None:
+    """The gemm arguments of rank's output frames, from the arguments `a` of the whole-clip conv3 call (padT = padL = 0,
+    ks = 1, stride = T, M = T * Ho * Wo; fp16 output).  None when the rank has no frame.
+
+    The result addresses the whole clip and the whole output (every rank holds both, or maps them): x.off skips to
+    the first input frame the rank reads (padL = max(0, t0 - 1)), y.off to its first output frame.  With `local_input`
+    the rank holds ONLY its input frames [in0, in0 + nin) in a buffer of its own: x.off stays as given and the extra keys
+    `in0` / `nin` say which frames to put there."""
+    cv = a["conv"]
+    if cv.get("kind") != "conv3" or (cv.get("ks") or 1) != 1 or cv.get("padT") or cv.get("padL"):
+        raise ValueError("conv3_frame_shard takes the arguments of a whole-clip conv3 call")
+    T, hw = int(cv["stride"]), int(cv["Ho"]) * int(cv["Wo"])
+    if a["M"] != T * hw: raise ValueError("conv3_frame_shard: M must be T * Ho * Wo")
+    t0, nf = shard_frames(T, rank, world)
+    if nf == 0: return None
+    padL = max(0, t0 - 1)
+    fx = int(cv["Hi"]) * int(cv["Wi"]) * int(cv["Ci"]) * 2                       # bytes of an input frame (fp16 THWC)
+    fy = hw * int(a["y"].get("ld") or a["N"]) * 2                                # bytes of an output frame
+    b = dict(a, M=nf * hw, conv=dict(cv, padT=t0, padL=padL),
+             x=dict(a["x"], off=(a["x"].get("off") or 0) + (0 if local_input else padL * fx)),
+             y=dict(a["y"], off=(a["y"].get("off") or 0) + t0 * fy))
+    if local_input: b["in0"], b["nin"] = padL, min(T - 1, t0 + nf) - padL + 1
+    return b
+
+
+def all_gather_frames(y_local, T: int, group=None):
+    """rank's output frames [nf][frame elements] -> the whole clip's [T][frame elements] on every rank (frame ranges as
+    shard_frames gives them; ranks may hold different frame counts, so the gather runs on blocks padded to the largest)"""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    q = -(-T // world)
+    pad = torch.zeros((q,) + tuple(y_local.shape[1:]), dtype=y_local.dtype, device=y_local.device)
+    pad[: y_local.shape[0]] = y_local
+    stage = torch.empty((world * q,) + tuple(y_local.shape[1:]), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(stage, pad, group=group)
+    parts = []
+    for r in range(world):
+        _, nf = shard_frames(T, r, world)
+        parts.append(stage[r * q: r * q + nf])
+    return torch.cat(parts, 0)

@@ -195,6 +195,30 @@ def test_conv3_tensor_core(gpu, oracle, clip):
             if x is not None: gpu.free(x)
 
 
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("clip", [dict(T=5, H=6, W=6, C=32, N=128), dict(T=6, H=8, W=16, C=64, N=128)], ids=["general kernel", "tensor-core kernel"])
+def test_conv3_split_by_frames_is_the_whole_clip(gpu, oracle, clip, world):
+    """the multi-GPU form of conv3: every rank's frame range (run here one after the other on one GPU) writes the bits of the
+    whole-clip call"""
+    O = oracle
+    T, H, W, C, N = (clip[k] for k in "THWCN")
+    X = O.round_f16(O.randn(T * H * W * C, 31)); Wt = O.round_f16(O.randn(N * 27 * C, 33, 0.03)); bias = O.randn(N, 35, 0.1)
+    xb, wb, bb = gpu.upload(P().toF16(X)), gpu.upload(P().toF16(Wt)), gpu.upload(bias)
+    n = T * H * W * N
+    ya, yb = gpu.buffer(n * 2), gpu.upload(np.full(n, 0xFFFF, np.uint16))
+    whole = {"w": {"enc": "f16", "buf": wb, "off": 0, "bytes": wb._pf, "rows": N, "cols": 27 * C}, "x": {"buf": xb}, "y": {"buf": ya}, "M": T * H * W, "N": N, "K": 27 * C,
+             "epi": "bias", "ev": {"buf": bb}, "conv": {"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": 0, "padL": 0, "ks": 1}}
+    try:
+        P().gemm(gpu, whole)
+        for r in range(world):
+            a = P().conv3_frame_shard(dict(whole, y={"buf": yb}), r, world)
+            if a is not None: P().gemm(gpu, a)
+        a_, b_ = gpu.read(ya, 0, n * 2).view(np.uint16), gpu.read(yb, 0, n * 2).view(np.uint16)
+        assert np.array_equal(a_, b_), "the frame shards DIFFER from the whole clip"
+    finally:
+        for b in (xb, wb, bb, ya, yb): gpu.free(b)
+
+
 def test_ref_converted_bf16_linear_q4(gpu, oracle):
     """a BF16 linear layer, converted to 4-bit, through the GEMM (test/kernels.test.js:198-209)"""
     O = oracle

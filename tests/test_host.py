@@ -1,6 +1,7 @@
 """Host-side logic that needs no GPU: the native library loads and exports every symbol include/p0p.h declares,
 its host codecs agree with the oracle bit for bit, the converter mirrors the reference's converter tests
 (test/convert.test.mjs), and the N-shard byte ranges reassemble the full problem (2 gloo ranks on CPU)."""
+import json
 import os
 import re
 import subprocess
@@ -204,6 +205,20 @@ for enc, pack in (('q4g32a.t64', O.pack_q4), ('q8g64s.t64', O.pack_q8)):
     assert np.array_equal(got, Yfull), enc
     got1 = P.all_gather_columns(torch.from_numpy(Yloc.view(np.float16).reshape(M, s['rows'])[:1].copy())).numpy().view(np.uint16).reshape(-1)
     assert np.array_equal(got1, Yfull[:N]), enc
+# conv3 split by output frames: each rank's chunk call (the oracle stands in for the device) and the gather of the frames
+T, H, W, C, N = 5, 4, 4, 32, 64
+Xc = O.to_f16(O.round_f16(O.randn(T * H * W * C, 31))); Wc = O.to_f16(O.round_f16(O.randn(N * 27 * C, 33, 0.03)))
+whole = {{"w": {{"enc": "f16"}}, "x": {{"off": 0}}, "y": {{"off": 0}}, "M": T * H * W, "N": N, "K": 27 * C,
+         "conv": {{"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": 0, "padL": 0, "ks": 1}}}}
+Yw = np.zeros(T * H * W * N, np.uint16)
+O.gemm(enc="f16", X=Xc, W=Wc, Y=Yw, M=T * H * W, N=N, K=27 * C, w_rows=N, w_cols=27 * C, conv=whole["conv"])
+a = P.conv3_frame_shard(whole, rank, world)
+t0, nf = P.shard_frames(T, rank, world)
+Yl = np.zeros(nf * H * W * N, np.uint16)
+O.gemm(enc="f16", X=Xc[a["x"]["off"] // 2:], W=Wc, Y=Yl, M=a["M"], N=N, K=27 * C, w_rows=N, w_cols=27 * C, conv=a["conv"])
+assert a["y"]["off"] == t0 * H * W * N * 2
+got = P.all_gather_frames(torch.from_numpy(Yl.view(np.float16).reshape(nf, H * W * N)), T).numpy().view(np.uint16).reshape(-1)
+assert np.array_equal(got, Yw), 'conv3 frames'
 dist.barrier(); dist.destroy_process_group()
 print('rank', rank, 'ok')
 """
@@ -219,3 +234,60 @@ def test_n_sharding_two_ranks_gloo(P, tmp_path):
     outs = [p.communicate(timeout=180)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} ok" in o, o
+
+
+@pytest.mark.parametrize("T,world", [(13, 8), (13, 2), (5, 3), (4, 8), (1, 2)])
+def test_conv3_frame_shards_cover_the_clip(P, oracle, T, world):
+    """the frame ranges tile [0, T); each rank's chunk arguments give, on the oracle, the frames of the whole-clip call bit for
+    bit - with the rank addressing the whole clip, and with the rank holding only its frames plus the halo"""
+    O = oracle
+    H, W, C, N = 3, 4, 32, 64
+    X = O.to_f16(O.round_f16(O.randn(T * H * W * C, 31))); Wt = O.to_f16(O.round_f16(O.randn(N * 27 * C, 33, 0.03)))
+    whole = {"w": {"enc": "f16"}, "x": {"off": 0}, "y": {"off": 0, "ld": N}, "M": T * H * W, "N": N, "K": 27 * C,
+             "conv": {"kind": "conv3", "Hi": H, "Wi": W, "Ci": C, "Ho": H, "Wo": W, "stride": T, "padT": 0, "padL": 0, "ks": 1}}
+    Yw = np.zeros(T * H * W * N, np.uint16)
+    O.gemm(enc="f16", X=X, W=Wt, Y=Yw, M=T * H * W, N=N, K=27 * C, w_rows=N, w_cols=27 * C, conv=whole["conv"])
+    cover, Ys, Yl = [], np.zeros_like(Yw), np.zeros_like(Yw)
+    fx = H * W * C
+    for r in range(world):
+        t0, nf = P.shard_frames(T, r, world); cover += list(range(t0, t0 + nf))
+        a = P.conv3_frame_shard(whole, r, world)
+        assert (a is None) == (nf == 0)
+        if a is None: continue
+        O.gemm(enc="f16", X=X[a["x"]["off"] // 2:], W=Wt, Y=Ys[a["y"]["off"] // 2:], M=a["M"], N=N, K=27 * C, w_rows=N, w_cols=27 * C, conv=a["conv"])
+        b = P.conv3_frame_shard(whole, r, world, local_input=True)
+        mine = X[b["in0"] * fx:(b["in0"] + b["nin"]) * fx].copy()                       # only the frames the rank reads
+        assert b["x"]["off"] == 0 and b["nin"] <= nf + 2
+        O.gemm(enc="f16", X=mine, W=Wt, Y=Yl[b["y"]["off"] // 2:], M=b["M"], N=N, K=27 * C, w_rows=N, w_cols=27 * C, conv=b["conv"])
+    assert cover == list(range(T))
+    assert np.array_equal(Ys, Yw) and np.array_equal(Yl, Yw)
+    with pytest.raises(ValueError): P.conv3_frame_shard(dict(whole, conv=dict(whole["conv"], ks=3)), 0, 2)
+
+
+def test_converter_command_line(P, oracle, tmp_path):
+    """the CLI (tools/convert.mjs:9-62): usage errors exit 2, --dry-run lists encodings, a run writes the shards and manifest that
+    convertSafetensors gives for the same file, and loadWeights-style reading of the folder sees the same tensors"""
+    import io
+    from p0pc0rn_kernels_b200 import convert_cli
+    O = oracle
+    T = {"blocks.0.attn.qkv.weight": {"dtype": "BF16", "shape": [192, 256], "data": O.to_bf16(O.randn(192 * 256, 1, 0.05))},
+         "blocks.0.norm.weight": {"dtype": "F32", "shape": [256], "data": O.randn(256, 5)},
+         "embed_tokens.weight": {"dtype": "BF16", "shape": [100, 64], "data": O.to_bf16(O.randn(100 * 64, 6))},
+         "ids": {"dtype": "I64", "shape": [4], "data": np.arange(4, dtype=np.int64)}}
+    src = tmp_path / "model.safetensors"; src.write_bytes(P.writeSafetensors(T).tobytes())
+    out, err = io.StringIO(), io.StringIO()
+    assert convert_cli.main([], out, err) == 2 and "usage" in err.getvalue()
+    assert convert_cli.main([str(src)], out, err) == 2                                   # no --out and no --dry-run
+    assert convert_cli.main([str(src), "--out", str(tmp_path / "o"), "--bits", "5"], out, err) == 2
+    out = io.StringIO()
+    assert convert_cli.main([str(src), "--dry-run", "--bits", "8"], out, err) == 0
+    listing = out.getvalue()
+    assert "q8g64s.t64" in listing and "f32" in listing and "f16" in listing
+    out = io.StringIO()
+    assert convert_cli.main([str(tmp_path), "--out", str(tmp_path / "o"), "--bits", "4", "--shard-mb", "512"], out, err) == 0          # a folder of .safetensors files
+    assert out.getvalue().startswith("converted 3 tensors") and "skipped 1 non-float tensors" in out.getvalue()
+    want = P.convertSafetensors(src.read_bytes(), {"bits": 4, "keep": __import__("re").compile("embed")})
+    man = json.load(open(tmp_path / "o" / "manifest.json"))
+    assert man["tensors"] == want["manifest"]["tensors"] and man["shards"] == want["manifest"]["shards"] and "created" in man
+    for sh in man["shards"]:
+        assert np.array_equal(np.fromfile(tmp_path / "o" / sh["file"], np.uint8), want["shards"][sh["file"]])
