@@ -277,7 +277,7 @@ def run_configs(args, P, torch, gpu, stream, dev, pk, rank, world):
             def call(): P.attention(gpu, {"q": {"buf": q}, "k": {"buf": k}, "v": {"buf": v}, "o": {"buf": o}, "Lq": L, "Lk": L, "Hq": H, "Hkv": H, "mode": 0})
             ms = graph_time(call, max(3, min(args.steps, 20)))
             fl = 4.0 * L * L * 128 * H
-            print(json.dumps({"config": "attention after dit_qkv (24 heads x 3600 tokens x 128, no mask)", "family": "mma.sync flash attention", "ms": ms,
+            print(json.dumps({"config": "attention after dit_qkv (24 heads x 3600 tokens x 128, no mask)", "family": {16: "warp-level mma.sync flash attention", 17: "tcgen05 flash attention (V transposed by a pre-pass, inside the timed call)"}.get(gpu.lastKernel), "ms": ms,
                               "TFLOP/s": fl / (ms * 1e-3) / 1e12, "frac_tensor": fl / (ms * 1e-3) / 1e12 / pk["tensor"]}), flush=True)
             for b in (q, k, v, o): gpu.free(b)
         elif name == "conv3":

@@ -27,7 +27,7 @@ XMODE = {"f16": 0, "lnmod": 1, "rms": 2, "conv": 3, "conv3": 4}
 EPI = {"f16": 0, "f32": 1, "resadd": 2, "swiglu": 3, "heads": 4, "bias": 5, "onormgate": 6}
 F_GATE, F_RES, F_STORE, F_GN, F_UP2, F_PN, F_BIAS, F_GELU, F_ROPE_HALF = 1, 2, 4, 8, 16, 32, 64, 128, 256
 K_AUTO, K_GENERIC, K_DECODE, K_UMMA = 0, 1, 2, 3
-KERNEL_NAMES = {0: "auto", 1: "generic", 2: "decode", 3: "umma"}
+KERNEL_NAMES = {0: "auto", 1: "generic", 2: "decode", 3: "umma", 16: "attention (warp-level)", 17: "attention (tcgen05)"}
 
 
 class Opts(C.Structure):

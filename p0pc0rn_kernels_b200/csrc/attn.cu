@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstddef>
+#include <cstdlib>
 
 #include "ctx.h"
 #include "device_once.h"
@@ -55,7 +56,11 @@ extern "C" int p0p_attention(p0p_ctx* c, const p0p_attn_args* a, double* flops) 
     k_attn_vt<<<dim3((Lk + 63u) / 64u, Hkv), 256, 0, c->stream>>>(p.V, reinterpret_cast<__half*>(c->scratch), Lk, ldv);
     AttnTcP t{};
     t.O = p.O; t.Lq = Lq; t.Lk = Lk; t.ldo = ldo; t.Hq = Hq; t.Hkv = Hkv; t.mode = a->mode; t.nvalid = nvalid; t.scale_log2 = p.scale_log2; t.status = c->dev_status;
-    k_attn_tc<<<dim3((Lq + 255u) / 256u, Hq), ATC_THREADS, ATC_SMEM, c->stream>>>(t, mq, mk, mv);
+    attn_plan(Lq, Lk, Hq, a->mode, nvalid, (uint32_t)c->prop.multiProcessorCount, t.np, t.ns);
+#ifdef P0P_KNOBS
+    if (const char* e = getenv("P0P_ATTN_NS")) { const uint32_t T = (Lq + 127u) / 128u; uint32_t s = (uint32_t)atoi(e); if (s <= T && ((T - s) & 1u) == 0u) { t.ns = s; t.np = (T - s) / 2u; } }
+#endif
+    k_attn_tc<<<Hq * (t.np + t.ns), ATC_THREADS, ATC_SMEM, c->stream>>>(t, mq, mk, mv);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(c, e, "attention launch");
     c->launches += 2;

@@ -3,7 +3,7 @@
 // V given TRANSPOSED, [Hkv][128][ldv] (a pre-pass makes that copy), so that both products take K-major operands:
 //   S = Q K^T   A = Q tile [128 q][128 d] (shared memory),  B = K tile [128 keys][128 d] (shared memory)
 //   O += P V    A = P tile [128 q][128 keys] (tensor memory), B = V^T tile [128 d][128 keys] (shared memory)
-// One block = two tiles of 128 queries of one head that share every K / V tile.  Tensor memory (512 columns x 128 lanes):
+// One block = two tiles of 128 queries of one head that share every K / V tile (or one tile: see attn_plan).  Tensor memory (512 columns x 128 lanes):
 // S of tile A | S of tile B | O of tile A | O of tile B, 128 fp32 columns each; lane = query row.  P (fp16, two keys per
 // column) is written over the first 64 columns of its S, which is free once the softmax threads hold the row.
 // Roles: warp 0 loads tiles by tensor-map copies into a ring of 32-KB slots (K0 V0 K1 V1 ...); warp 1 issues the
@@ -17,6 +17,10 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <algorithm>
+#include <functional>
+#include <vector>
+
 #include "sync.cuh"
 #include "umma.cuh"
 
@@ -25,6 +29,7 @@ namespace p0p {
 struct AttnTcP {
   __half* O;
   uint32_t Lq, Lk, ldo, Hq, Hkv, mode, nvalid;
+  uint32_t np, ns;       // per head: np blocks of two query tiles, then ns blocks of one (2 * np + ns = tiles of 128 queries)
   float scale_log2;      // scale * log2(e)
   int* status;           // bounded waits report here
 };
@@ -32,7 +37,27 @@ struct AttnTcP {
 constexpr uint32_t ATC_THREADS = 320u, ATC_TILE = 32768u, ATC_SLOTS = 4u;
 constexpr uint32_t ATC_SMEM = 1024u + (2u + ATC_SLOTS) * ATC_TILE + 256u;      // alignment slack + Q tiles + ring + barriers
 
+#ifndef ATC_EMU
+#define ATC_EMU 6          // of every 16 pairs of scores, how many take their exponential on the FMA pipe instead of the MUFU
+                           // (24 heads x 3600 x 3600: 0 -> 193 us, 4 -> 186, 6 -> 183, 8 -> 207)
+#endif
+
 __device__ __forceinline__ float atc_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+// 2^t for a pair, without the special-function unit (16 results per clock per SM, the softmax's bound): t = n + f with
+// n = floor(t); 2^f by a cubic (least-maximum relative error 8.6e-5, below the half-ulp of the fp16 the result is rounded
+// to), then n is added into the exponent field.  (t + 1.5 * 2^23) rounded down holds n in its low mantissa bits; shifted
+// left by 23 that is n in the exponent position (the constant's own bits shift out).  The cubic is >= 1, so n >= -126 keeps
+// the sum a valid float.
+__device__ __forceinline__ float2 atc_ex2_poly2(float2 t) {
+  t.x = fmaxf(t.x, -126.0f); t.y = fmaxf(t.y, -126.0f);
+  const float2 r = __fadd2_rd(t, make_float2(12582912.0f, 12582912.0f));
+  const float2 fl = __fadd2_rn(r, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = __ffma2_rn(fl, make_float2(-1.0f, -1.0f), t);
+  float2 q = __ffma2_rn(f, make_float2(0.07706704f, 0.07706704f), make_float2(0.22764499f, 0.22764499f));
+  q = __ffma2_rn(q, f, make_float2(0.69511679f, 0.69511679f));
+  q = __ffma2_rn(q, f, make_float2(1.0f, 1.0f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23)), __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23)));
+}
 
 __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                                                             const __grid_constant__ CUtensorMap mapV) {
@@ -43,11 +68,14 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
   const uint32_t q_full = bars, kv_full = bars + 8u, kv_empty = kv_full + 8u * ATC_SLOTS, s_full = kv_empty + 8u * ATC_SLOTS;
   const uint32_t p_full = s_full + 16u, o_full = p_full + 16u, tmem_slot = o_full + 16u;
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-  const uint32_t h = blockIdx.y, hk = h / (p.Hq / p.Hkv), q0 = blockIdx.x * 256u;
-  const bool hasB = q0 + 128u < p.Lq;
+  // the grid: first every head's two-tile blocks, then every head's one-tile blocks (the short ones fill the last wave)
+  const bool hasB = blockIdx.x < p.Hq * p.np;
+  const uint32_t b1 = blockIdx.x - p.Hq * p.np;
+  const uint32_t h = hasB ? blockIdx.x / p.np : b1 / p.ns, q0 = hasB ? (blockIdx.x - h * p.np) * 256u : (2u * p.np + (b1 - h * p.ns)) * 128u;
+  const uint32_t hk = h / (p.Hq / p.Hkv);
   // keys any row of this block can see, and the key tiles that covers                        (attention.js:64)
   uint32_t kEnd = p.Lk;
-  if (p.mode == 1u) kEnd = min(p.Lk, min(q0 + 255u, p.nvalid - 1u) + 1u);
+  if (p.mode == 1u) kEnd = min(p.Lk, min(q0 + (hasB ? 255u : 127u), p.nvalid - 1u) + 1u);
   if (p.mode == 2u) kEnd = min(p.Lk, p.nvalid);
   const uint32_t nj = (kEnd + 127u) >> 7;
 
@@ -173,21 +201,24 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
           }
           m_used = m_new;
         }
-        float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const float nm = -m_used;
+        float2 ls[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+        const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_used, -m_used);
 #pragma unroll
         for (int c = 0; c < 4; c++) {
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; e++) {
-            const float p0 = atc_ex2(fmaf(__uint_as_float(s[32 * c + 2 * e]), sc, nm)), p1 = atc_ex2(fmaf(__uint_as_float(s[32 * c + 2 * e + 1]), sc, nm));
-            ls[e & 3] += p0 + p1;
-            const __half2 hp = __floats2half2_rn(p0, p1);
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(s[32 * c + 2 * e]), __uint_as_float(s[32 * c + 2 * e + 1])), sc2, nm2);
+            float2 pr;
+            if ((e * ATC_EMU) % 16 < ATC_EMU) pr = atc_ex2_poly2(t);                              // spread evenly over the chunk
+            else pr = make_float2(atc_ex2(t.x), atc_ex2(t.y));
+            ls[e & 1] = __fadd2_rn(ls[e & 1], pr);
+            const __half2 hp = __floats2half2_rn(pr.x, pr.y);
             pk[e] = *reinterpret_cast<const uint32_t*>(&hp);
           }
           tmem_st16(s_addr + 16u * c, pk);
         }
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        l += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -225,6 +256,37 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512u); }
+}
+
+// How a head's T tiles of 128 queries are cut into blocks.  Two-tile blocks are the efficient ones (K / V tiles shared, the
+// softmax of one tile hidden behind the multiplies of the other), but blocks are handed to SMs whole: 15 two-tile blocks
+// per head x 24 heads on 148 SMs is 2.4 rounds, of which the third is mostly idle.  One-tile blocks cost ATC_SINGLE_COST of a
+// two-tile block (measured: with nothing to overlap its softmax with, one tile takes 0.85 of the time of two) and fill that
+// last round.  The plan simulates the hardware's in-order hand-out for every split and keeps
+// the shortest; cost of a block = its key tiles (they differ under the causal mask).
+constexpr double ATC_SINGLE_COST = 0.85;
+inline void attn_plan(uint32_t Lq, uint32_t Lk, uint32_t Hq, uint32_t mode, uint32_t nvalid, uint32_t sms, uint32_t& np, uint32_t& ns) {
+  const uint32_t T = (Lq + 127u) / 128u;
+  np = T / 2u; ns = T & 1u;
+  if ((uint64_t)Hq * T > 64ull * sms || sms == 0u) return;         // many rounds: the last one hardly matters
+  // the answer depends on these seven numbers only, and a model asks for the same ones call after call
+  struct Key { uint32_t v[6]; uint32_t np, ns; };
+  static thread_local Key memo = {{0, 0, 0, 0, 0, 0}, 0, 0};
+  const uint32_t key[6] = {Lq, Lk, Hq, mode, nvalid, sms};
+  if (std::equal(key, key + 6, memo.v)) { np = memo.np; ns = memo.ns; return; }
+  auto keys = [&](uint32_t q_last) { uint32_t e = Lk; if (mode == 1u) e = std::min(Lk, std::min(q_last, nvalid - 1u) + 1u); if (mode == 2u) e = std::min(Lk, nvalid); return (e + 127u) / 128u; };
+  double best = 1e300;
+  std::vector<double> heap(sms);
+  for (uint32_t s = T & 1u; s <= T && s <= (T & 1u) + 16u; s += 2u) {
+    const uint32_t n2 = (T - s) / 2u;
+    std::fill(heap.begin(), heap.end(), 0.0);                       // min-heap of the SMs' finish times (all equal: already a heap)
+    auto give = [&](double cost) { std::pop_heap(heap.begin(), heap.end(), std::greater<double>()); heap.back() += cost; std::push_heap(heap.begin(), heap.end(), std::greater<double>()); };
+    for (uint32_t h = 0; h < Hq; h++) for (uint32_t i = 0; i < n2; i++) give((double)keys(i * 256u + 255u));
+    for (uint32_t h = 0; h < Hq; h++) for (uint32_t i = 0; i < s; i++) give(ATC_SINGLE_COST * keys((2u * n2 + i) * 128u + 127u));
+    const double span = *std::max_element(heap.begin(), heap.end());
+    if (span < best * 0.995) { best = span; np = n2; ns = s; }
+  }
+  std::copy(key, key + 6, memo.v); memo.np = np; memo.ns = ns;
 }
 
 // V [Hkv][Lk][128] -> V^T [Hkv][128][ldv] (ldv >= Lk, a multiple of 8): 64 keys x 128 dims per block through shared memory
