@@ -157,7 +157,8 @@ uint64_t p0p_launch_count(const p0p_ctx* ctx);
  * synchronisation).  It takes no context: w, x, y are the caller's own device pointers (16-byte aligned), work is
  * enqueued on the caller's cudaStream_t, and it calls no allocating routine.  The kernel's split-K partial sums
  * live in an array of P0P_STATIC_SCRATCH_BYTES built into the library's device image (every GPU that loads the
- * library holds it until the process exits); a shape that needs more (roughly 4 * M * N * ceil(K / 1024) bytes)
+ * library holds it until the process exits); a shape that needs more (8 * M * N * ceil(K / 2048) bytes; above 8 tokens
+ * 8 * M * N * ceil(K / 1024))
  * is refused with a message in `err`.  All calls on a device share that array: calls whose kernels overlap on
  * the GPU race, so keep them in one stream order.  The first call on each device resolves the array's device
  * address; make it before any stream capture.  Conditions: 1 <= M <= 16, N % 64 == 0, K % 256 == 0.

@@ -48,19 +48,26 @@ uint64_t plan_decode(DecodeP& d, DecodeLaunch& L, int sms, size_t smem_per_sm) {
   if (p.epi != P0P_EPI_SWIGLU && d.th > avail) d.th = avail;
   d.tiles = p.epi == P0P_EPI_SWIGLU ? 2u * d.th : d.th;
   d.nslots = d.tiles * 64u;
-  // k-block: as long as the token tile allows (about 32 KB), short enough for ~4 units per SM
+  // k-block: as long as the token tile allows (about 32 KB); the blocks share the stages evenly whatever its length, but a
+  // block's range must be at least one unit long (a unit is shared by at most two blocks), and every block wants work
   uint32_t kc = p.M <= 8u ? 2048u : 1024u;                                // token tile of (M + 1) * kc fp16 stays near 32 KB
-  const uint64_t want_units = 4ull * (uint64_t)sms;
-  while (kc > 256u && (uint64_t)d.tiles * ((p.K + kc - 1u) / kc) < want_units) kc >>= 1;
-  if (kc > p.K) kc = p.K;
+  while (kc > p.K) kc >>= 1;                                              // (K is a multiple of 256)
+  d.T = d.tiles * (p.K / (uint32_t)D_STAGE_K);
+  const uint32_t tok_stride0 = kc * 2u + 64u;
+  const size_t smem0 = (size_t)D_STAGES * D_STAGE_BYTES_Q8 + (size_t)(p.M + 1u) * tok_stride0 + 16384u;      // upper estimate: how many blocks an SM holds
+  const uint32_t slots = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, smem_per_sm / (smem0 + 1024))) * (uint32_t)sms;
+  while (kc > (uint32_t)D_STAGE_K && d.T / std::min(d.T, slots) < kc / (uint32_t)D_STAGE_K) kc >>= 1;
   d.KC = kc; d.S = (p.K + kc - 1u) / kc; d.units = d.tiles * d.S;
   const uint32_t tok_stride = d.KC * 2u + (p.enc == P0P_ENC_Q4 ? 64u : 16u);
   const size_t ct_bytes = p.enc == P0P_ENC_Q4 ? (size_t)(d.KC / 32u) * (d.Mp / 2u) * 24u : (size_t)(d.KC / 64u) * (d.Mp / 2u) * 16u;
   L.smem = (size_t)D_STAGES * (p.enc == P0P_ENC_Q4 ? D_STAGE_BYTES_Q4 : D_STAGE_BYTES_Q8) + (((p.M + 1u) * tok_stride + 127u) & ~127u) + ct_bytes + 4u * 32u * (d.Mp / 2u) * 4u + 2u * D_STAGES * 8u + 128u;
   const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, smem_per_sm / (L.smem + 1024)));
-  L.grid = (int)std::min<uint64_t>(d.units, (uint64_t)per_sm * (uint64_t)sms);      // every block is resident: the unit ranges run side by side
+  // every block is resident: the ranges run side by side.  At least KC / 256 stages per block (see above).
+  L.grid = (int)std::min<uint64_t>(d.T / (d.KC / (uint32_t)D_STAGE_K), (uint64_t)per_sm * (uint64_t)sms);
+  while ((uint64_t)d.T * (uint64_t)L.grid >= (1ull << 32)) L.grid = (L.grid + 1) / 2;      // the kernels' range arithmetic is 32-bit
+  d.G = (uint32_t)L.grid;
   L.fin_blocks = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u : (((p.N + 3u) & ~3u) + 127u) / 128u;
-  return (uint64_t)d.S * p.M * d.nslots * 4ull;
+  return 2ull * d.S * p.M * d.nslots * 4ull;
 }
 
 cudaError_t launch_decode_pair(const DecodeP& d, const DecodeLaunch& L, int device, cudaStream_t st) {

@@ -1,8 +1,12 @@
 // Decode-sized multiply (up to 16 tokens, the library's own choice up to 8; q4 / q8 weights): the call is bound by
 // streaming the weights out of HBM once, so the kernel is built around that stream.
 //
-//   stage 1  k_decode_stream   The (64-row tile) x (k-block) units of the weight are spread evenly over a grid of
-//            about three blocks per SM.  In each block one producer lane moves whole records from global to
+//   stage 1  k_decode_stream   The weight is cut into (64-row tile) x (k-block) units, a unit into stages of 256 k; the
+//            stages, in unit order, are dealt out evenly to a grid of about three blocks per SM: every block gets the
+//            same number of stages (+-1), so a block's range may begin and end inside a unit, and a unit may be shared
+//            by two blocks (never three: a range is at least a unit long).  Handing out whole units instead left the
+//            LLM block's shapes (896 units on 444 blocks) with a few blocks that had 3 units against 2.
+//            In each block one producer lane moves whole records from global to
 //            shared memory with bulk asynchronous copies (cp.async.bulk, mbarrier-tracked, a ring of stages);
 //            eight consumer warps: four row groups of 16 rows, two warps each that split a stage's records.
 //            Codes go to the tensor cores WITHOUT being dequantised.  A 4-bit code q is left where it sits and read as
@@ -14,9 +18,11 @@
 //            where Sx (the sum of the group's tokens) depends only on the tokens and is tabulated once per k-block
 //            (q8: as the accumulator's starting value).  The tokens are staged in shared memory in the operand order
 //            of the instruction, with the fused prologue (plain fp16 / RMSNorm / LayerNorm+modulation)
-//            applied on the way in.  Each unit's 64 x M partial sums go to a scratch buffer.
-//   stage 2  k_decode_finish   sums the k-block partials in a fixed order (deterministic, no atomics) and
-//            applies the fused epilogue.
+//            applied on the way in.  The 64 x M partial sums of each unit, or of each part of a shared unit, go to a
+//            scratch buffer: part 0 = the part that starts at the unit's first stage, part 1 = the rest.
+//   stage 2  k_decode_finish   sums the partials in a fixed order (k-block by k-block, part 0 then part 1; which units have
+//            a part 1 follows from the same arithmetic that dealt out the stages: deterministic, no atomics, nothing to
+//            clear) and applies the fused epilogue.
 // Both kernels are launched as programmatic dependents: stage 2 is resident before stage 1 ends, and the next call's
 // stage 1 streams its first weights while this call's stage 2 still runs; each waits (griddepcontrol.wait) before it
 // touches what the kernel before it writes.
@@ -47,7 +53,8 @@ struct DecodeP {
   uint32_t KC, S;     // k-block length (multiple of 128) and count
   uint32_t units;     // tiles * S
   uint32_t nslots;    // tiles * 64
-  float* scratch;     // [S][M][nslots] fp32
+  uint32_t T, G;      // stages of the whole call (tiles * K / 256) and blocks of the stream kernel: block b takes stages [b*T/G, (b+1)*T/G)
+  float* scratch;     // [S][2 parts][M][nslots] fp32
   int* status;
   uint32_t vec32;     // fp32 tokens and the prologue vector may be read with 16-byte loads
 };
@@ -56,6 +63,25 @@ struct DecodeP {
 __device__ __forceinline__ uint32_t d_tile_row0(const DecodeP& d, uint32_t t) {
   if (d.p.epi == P0P_EPI_SWIGLU) return t < d.th ? d.p.wR0 + t * 64u : d.p.wR1 + (t - d.th) * 64u;
   return d.p.wR0 + t * 64u;
+}
+
+// Stage i of the call, in unit order (k-block by k-block, tile by tile, then along k): which unit, and where in it.
+struct DSeg { uint32_t kb, t, st, spk; };       // k-block, tile, stage within the unit, stages of this k-block's units
+__device__ __forceinline__ DSeg d_seg(const DecodeP& d, uint32_t i) {
+  const uint32_t spk = d.KC / (uint32_t)D_STAGE_K, per_kb = d.tiles * spk;
+  DSeg g;
+  g.kb = min(i / per_kb, d.S - 1u);
+  const uint32_t rem = i - g.kb * per_kb;
+  g.spk = min(d.KC, d.p.K - g.kb * d.KC) / (uint32_t)D_STAGE_K;               // the last k-block may be shorter
+  g.t = rem / g.spk; g.st = rem - g.t * g.spk;
+  return g;
+}
+// (T * G stays below 2^32: the plan sees to it, so that these divisions are 32-bit ones — the second stage does two per k-block)
+__device__ __forceinline__ uint32_t d_range(const DecodeP& d, uint32_t b) { return (b * d.T) / d.G; }
+// does a block boundary fall strictly inside the unit that spans stages [u0, u0 + n)?  (then the unit has a part 1)
+__device__ __forceinline__ bool d_unit_split(const DecodeP& d, uint32_t u0, uint32_t n) {
+  const uint32_t b = ((u0 + 1u) * d.G + d.T - 1u) / d.T;                         // the first boundary above u0
+  return b < d.G && d_range(d, b) < u0 + n;
 }
 
 // ---- token staging: one thread per (token, 8 consecutive k): 16-byte loads, the fused prologue, 16 bytes of operand.
@@ -248,7 +274,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   __syncthreads();
   grid_launch_dependents();                 // the second stage may be brought onto the SMs now; it waits for this grid to finish
 
-  const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * d.units) / gridDim.x), u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * d.units) / gridDim.x);
+  const uint32_t i0 = d_range(d, blockIdx.x), i1 = d_range(d, blockIdx.x + 1u);      // this block's stages
   constexpr uint32_t REC = ENC == P0P_ENC_Q4 ? 1280u : 4224u, REC_K = ENC == P0P_ENC_Q4 ? 32u : 64u;
   constexpr uint32_t STAGE_TX = (D_STAGE_K / REC_K) * REC;              // a k-block is a whole number of stages (K % 128 == 0)
   constexpr uint32_t RPW = (D_STAGE_K / REC_K) / 2u;                    // records of a stage per consumer warp (two warps share 16 rows)
@@ -257,17 +283,18 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
     // ------------------------------------------------------------------ producer: one lane streams the records
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      for (uint32_t u = u0; u < u1; u++) {
-        const uint32_t kb = u / d.tiles, t = u % d.tiles;
-        const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
-        const uint32_t r0 = d_tile_row0(d, t);
-        const unsigned char* src = p.W + ((size_t)(r0 >> 6) * p.wG + (p.wk0 + k_beg) / REC_K) * REC;
-        for (uint32_t k = 0; k < klen; k += D_STAGE_K, src += STAGE_TX) {
+      for (uint32_t i = i0; i < i1;) {
+        const DSeg sg = d_seg(d, i);
+        const uint32_t n = min(i1 - i, sg.spk - sg.st);                           // stages of this unit in the block's range
+        const uint32_t r0 = d_tile_row0(d, sg.t);
+        const unsigned char* src = p.W + ((size_t)(r0 >> 6) * p.wG + (p.wk0 + sg.kb * d.KC + sg.st * D_STAGE_K) / REC_K) * REC;
+        for (uint32_t q = 0; q < n; q++, src += STAGE_TX) {
           if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, d.status, 101, 200u)) return;
           mbar_expect_tx(full0 + 8u * s, STAGE_TX);
           bulk_g2s(smem_u32(stages + s * D_STAGE_BYTES), src, STAGE_TX, full0 + 8u * s);
           if (++s == D_STAGES) { s = 0; ph ^= 1u; }
         }
+        i += n;
       }
     }
     return;
@@ -299,9 +326,13 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
   grid_dependency_wait();
   // `ok` turns false when a bounded wait ran out: the warp then skips all work but still meets the others at
   // the named barriers below, so nobody is left waiting for it.
-  for (uint32_t u = u0; u < u1; u++) {
-    const uint32_t kb = u / d.tiles, t = u % d.tiles;
-    const uint32_t k_beg = kb * d.KC, klen = min(d.KC, p.K - k_beg);
+  for (uint32_t si = i0; si < i1;) {
+    const DSeg sg = d_seg(d, si);
+    const uint32_t nst = min(i1 - si, sg.spk - sg.st);
+    si += nst;
+    const uint32_t kb = sg.kb, t = sg.t;
+    const uint32_t k_beg = kb * d.KC, klen = sg.spk * D_STAGE_K, kfrom = sg.st * D_STAGE_K, kto = kfrom + nst * D_STAGE_K;
+    const uint32_t part = sg.st ? 1u : 0u;
     if (kb != cur_kb) {                       // a new k-block: restage the tokens (all consumers are past the old ones)
       bar_sync_named(1, D_CONSUMERS);
       if (ok) d_stage_tokens<ENC, XMODE, MP>(d, k_beg, klen, xs, ctc, cts, tok_stride, tid);
@@ -314,7 +345,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 #pragma unroll
       for (int i = 0; i < 4; i++) { tot[h][i] = 0.0f; tmn[h][i] = 0.0f; }
 
-    for (uint32_t k = 0; ok && k < klen; k += D_STAGE_K) {
+    for (uint32_t k = kfrom; ok && k < kto; k += D_STAGE_K) {
       if (!mbar_wait(full0 + 8u * s, ph, d.status, 102)) { ok = false; break; }
       const uint32_t so = anchor(s * D_STAGE_BYTES), ko = anchor(k);
       const uint32_t ca = code0 + so, sa = sm0 + so;
@@ -336,7 +367,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
       if (++s == D_STAGES) { s = 0; ph ^= 1u; }
     }
     // ---- the two warps of a row group add up (through shared memory), then this unit's partial sums go to
-    // scratch[kb][token][slot].  Both named barriers are met in drain mode too.
+    // scratch[kb][part][token][slot].  Both named barriers are met in drain mode too.
     if (ENC == P0P_ENC_Q4) {
 #pragma unroll
       for (int h = 0; h < MP / 8; h++)
@@ -356,7 +387,7 @@ __global__ void __launch_bounds__(D_THREADS) k_decode_stream(const DecodeP d) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
           const uint32_t tok = 2u * t4 + (i & 1) + 8u * h, row = (i & 2) ? rlo + 8u : rlo;
-          if (tok < p.M) d.scratch[((size_t)kb * p.M + tok) * d.nslots + t * 64u + row] = v[i];
+          if (tok < p.M) d.scratch[((size_t)(kb * 2u + part) * p.M + tok) * d.nslots + t * 64u + row] = v[i];
         }
       }
     }
@@ -376,19 +407,31 @@ __global__ void __launch_bounds__(128) k_decode_finish(const DecodeP d) {
   else slot = col;
   slot = min(slot, d.nslots - 1u);
   grid_dependency_wait();                       // the partial sums come from the stream kernel this launch may overlap with
-  // the partials of one output are read in batches of eight independent loads, then added in k-block order
+  // the partials of one output are read in batches of eight independent loads (a unit's part 1 only where the unit was
+  // shared by two blocks), then added in k-block order
+  const uint32_t tile = slot >> 6, spk = d.KC / (uint32_t)D_STAGE_K;
   float acc[MP];
 #pragma unroll
   for (int j = 0; j < MP; j++) acc[j] = 0.0f;
   for (uint32_t kb0 = 0; kb0 < d.S; kb0 += 8u) {
+    uint32_t two = 0u;                                            // bit i: k-block kb0 + i has a part 1 for this column's tile
+#pragma unroll
+    for (uint32_t i = 0; i < 8u; i++) {
+      const uint32_t kb = min(kb0 + i, d.S - 1u), n = min(d.KC, p.K - kb * d.KC) / (uint32_t)D_STAGE_K;
+      if (kb0 + i < d.S && d_unit_split(d, kb * d.tiles * spk + tile * n, n)) two |= 1u << i;
+    }
 #pragma unroll
     for (int j = 0; j < MP; j++) {
       if ((uint32_t)j < p.M) {
-        float v[8];
+        float v[8], w[8];
 #pragma unroll
-        for (uint32_t i = 0; i < 8u; i++) v[i] = kb0 + i < d.S ? __ldcg(d.scratch + ((size_t)(kb0 + i) * p.M + j) * d.nslots + slot) : 0.0f;
+        for (uint32_t i = 0; i < 8u; i++) {
+          const float* src = d.scratch + ((size_t)((kb0 + i) * 2u) * p.M + j) * d.nslots + slot;
+          v[i] = kb0 + i < d.S ? __ldcg(src) : 0.0f;
+          w[i] = (two >> i) & 1u ? __ldcg(src + (size_t)p.M * d.nslots) : 0.0f;
+        }
 #pragma unroll
-        for (uint32_t i = 0; i < 8u; i++) acc[j] += v[i];
+        for (uint32_t i = 0; i < 8u; i++) { acc[j] += v[i]; acc[j] += w[i]; }
       }
     }
   }

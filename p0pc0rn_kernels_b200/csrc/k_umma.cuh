@@ -21,10 +21,12 @@
 //                              exactness test is redone in fp32 by its own lane), written straight into tensor memory
 //                              (tcgen05.st): the multiply takes A from there
 //   last warp       records    bulk copies of the quantised records (two 64-row record tiles x up to 256 k per copy pair)
-// Tensor memory: 384 accumulator columns + four 32-column operand stages (quantised weights), or 512 accumulator columns
-// (fp16 weights, both operands in shared memory).  The accumulator columns hold two tiles of up to 192 tokens (the next
-// tile's multiply overlaps the epilogue), or one tile of up to 384, or 2 / 4 accumulators of one narrow tile that take the
-// 16-k multiplies in turn (see launch_umma for why).  gate|up (swiglu) tiles interleave gate and up rows in the A tile, so
+// Tensor memory (512 columns): the accumulators first - two buffers for tiles up to 128 tokens (the next tile's multiplies
+// overlap the epilogue), one beyond - then the dequantised operand's stages in every column behind them (quantised weights),
+// or two accumulator buffers of 256 columns (fp16 weights, both operands in shared memory).  A tile has ONE accumulator:
+// consecutive multiplies into the same accumulator issue back to back at the tensor pipe's rate (measured: 8.7 cycles each
+// at 16 tokens, 114 at 256, whether they alternate between accumulators or not).  gate|up (swiglu) tiles interleave gate and
+// up rows in the A tile, so
 // that (gate, up) of one output sit in adjacent lanes.  RMSNorm / LayerNorm+modulation prologues are applied by a one-pass
 // kernel into an fp16 scratch copy of the tokens (the same token tile would otherwise be re-normalised by every column
 // tile).  Few output columns: the k loop is split into units whose partial sums k_umma_finish adds (split-K).
@@ -57,7 +59,9 @@ struct UmmaP {
   uint32_t KSPLIT;      // accumulators per tile that take the 16-k multiplies in turn (1, 2 or 4), summed by the epilogue
   uint32_t NS;          // stages of the token ring (2 .. 8)
   uint32_t KW;          // k-steps of 64 k per pipeline step (1 or 2)
-  uint32_t NA;          // stages of the dequantised operand in tensor memory (NA * KW <= 4); fp16 weights: = NS
+  uint32_t NA;          // stages of the dequantised operand in tensor memory (a_col0 + NA * KW * 32 <= 512, NA <= 8); fp16 weights: = NS
+  uint32_t acc_stride;  // tensor-memory columns from one accumulator buffer to the next
+  uint32_t a_col0;      // first tensor-memory column of the operand stages (quantised weights): the accumulators end there
   uint32_t LOCK;        // 1: the token ring and the operand ring advance together and share their barriers (NA == NS)
   uint32_t NQ;          // stages of quantised records (each KSUP k-steps long)
   uint32_t n_tiles, m_tiles;
@@ -112,16 +116,13 @@ struct Ring {
 
 // Quantised weights: the dequantised operand lives in tensor memory (written with tcgen05.st) instead of shared memory.
 // Shared-memory bandwidth is what bounds the kernel otherwise: per 64-k step a 128 x 64 fp16 tile would be
-// written once and read once there, on top of the token tile and the records.  Tensor memory then holds 384
-// accumulator columns and four 32-column operand stages (384 + 4 x 32 = 512).  The accumulator columns are two
-// tiles of up to 192 tokens (the next tile's multiply overlaps the epilogue) or ONE tile of up to 384 tokens: the
-// dequantisation of a weight block costs the same whatever the tile's width, so a wide tile halves that cost per
-// token, which is worth more than the overlap whenever M gives the wide tile enough tokens.
+// written once and read once there, on top of the token tile and the records.  The dequantisation of a weight block costs
+// the same whatever the tile's width, so a wide tile (up to 384 tokens as two multiplies of 192) halves that cost per token.
 // fp16 weights: both operands in shared memory (TMA), 512 accumulator columns.
 //
 // EPI: the fused epilogue, a compile-time constant.  One instantiation per (encoding, epilogue): a kernel that carries
 // all seven epilogues is ~470 KB of code, most of it never run by a given launch.
-constexpr uint32_t U_ACC_STRIDE_ATM = 192, U_A_COL0_ATM = 384;
+constexpr uint32_t U_NA_MAX = 8;         // most operand stages in tensor memory
 constexpr uint32_t U_DEQ_WARPS = 8;      // two groups of four
 constexpr uint32_t U_NX_MAX = 8;         // most stages of the token ring
 // Pipeline steps.  One step covers KW k-steps of 64 k (KW = 1 or 2, chosen per launch): every hand-over between the roles - a
@@ -156,13 +157,13 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t XT = BT * 128u, XS = KW * XT;                                     // bytes of a token sub-tile (64 k) and of a stage
   const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * XS;
-  const uint32_t acc_stride = ATM ? U_ACC_STRIDE_ATM : 256u;
+  const uint32_t acc_stride = u.acc_stride;
   const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * UQ<ENC>::STAGE);
   const uint32_t bars = epi_sh + (uint32_t)U_EPI_BYTES;
   float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
   // barrier slots (8 bytes each)
-  const uint32_t xfull = bars, xempty = xfull + 8u * U_NX_MAX, afull = xempty + 8u * U_NX_MAX, aempty = afull + 8u * 4u;
-  const uint32_t wq_full = aempty + 8u * 4u, wq_empty = wq_full + 8u * U_NQ_MAX;
+  const uint32_t xfull = bars, xempty = xfull + 8u * U_NX_MAX, afull = xempty + 8u * U_NX_MAX, aempty = afull + 8u * U_NA_MAX;
+  const uint32_t wq_full = aempty + 8u * U_NA_MAX, wq_empty = wq_full + 8u * U_NQ_MAX;
   const uint32_t acc_full = wq_empty + 8u * U_NQ_MAX, acc_empty = acc_full + 16u, tmem_slot = acc_empty + 16u;
   const uint32_t NA = u.NA;                                                       // operand stage of step g: g % NA, its parity: (g / NA) & 1
   const uint32_t pfull = lock ? afull : xfull, pempty = lock ? aempty : xempty;   // the barriers the token producer works with
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   if (tid == 0) {
     for (uint32_t s = 0; s < U_NX_MAX; s++) { mbar_init(xfull + 8u * s, 1u); mbar_init(xempty + 8u * s, 1u); }      // the producer's expect_tx arrival / the multiplies' commit
-    for (uint32_t s = 0; s < 4u; s++) { mbar_init(afull + 8u * s, (ATM ? 4u * KW : 0u) + (lock ? 1u : 0u)); mbar_init(aempty + 8u * s, 1u); }       // the dequantisation warps of a step (+ the token producer) / the commit
+    for (uint32_t s = 0; s < U_NA_MAX; s++) { mbar_init(afull + 8u * s, (ATM ? 4u * KW : 0u) + (lock ? 1u : 0u)); mbar_init(aempty + 8u * s, 1u); }       // the dequantisation warps of a step (+ the token producer) / the commit
     for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, U_DEQ_WARPS); }
     for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
     fence_mbar_init();
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
 #pragma unroll
         for (uint32_t j = 0; j < KW; j++) {
           bd[j] = umma_desc_sw128(x_st + r.s * XS + j * XT);
-          at[j] = tmem_base + U_A_COL0_ATM + (as * KW + j) * 32u;
+          at[j] = tmem_base + u.a_col0 + (as * KW + j) * 32u;
           ad[j] = umma_desc_sw128(a_st + (r.s * KW + j) * U_A_BYTES);
         }
         const uint32_t first = k0 - kb;                             // 0 on the unit's first k-step: the first multiply overwrites
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     const uint32_t tile_off = tsel * (UQ<ENC>::KSUP * UQ<ENC>::RB + 64u);
     const uint32_t rec_row = tile_off + (ENC == P0P_ENC_Q4 ? rr * 16u : rr * 64u);
     const uint32_t rec_sm = tile_off + (ENC == P0P_ENC_Q4 ? 1024u + rr * 4u : 4096u + rr * 2u);
-    const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + U_A_COL0_ATM;
+    const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + u.a_col0;
     const uint32_t sub = KW == 2u ? grp : 0u, stride = KW == 2u ? 1u : 2u;
     // this group's steps are every `stride`-th of the running count of steps; their operand stage walks the ring of NA with them
     uint32_t as = KW == 2u ? 0u : grp, aph = 0u;

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include "k_umma.cuh"
 #include "tmap.h"
@@ -144,7 +145,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
       const uint64_t epi_tok = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? 150u : p.epi == P0P_EPI_SWIGLU ? 30u : 24u;
       // (with two accumulators the epilogue hides behind the next tile's k loop unless it is the longer of the two; it runs
       // about half as fast there, sharing the issue slots with the dequantisation)
-      const uint64_t per_tile = (atm && cand > 192u) ? (uint64_t)KSn * kstep + epi_tok * cand : std::max<uint64_t>((uint64_t)KSn * kstep, 2u * epi_tok * cand);
+      const uint64_t per_tile = (atm && cand > 128u) ? (uint64_t)KSn * kstep + epi_tok * cand : std::max<uint64_t>((uint64_t)KSn * kstep, 2u * epi_tok * cand);
       // Rounds of tiles over the SMs.  Fewer tiles than SMs: split-K (below) spreads their k loops over all SMs, so what counts
       // is the total work, not one round of it.  A last round that is not full is split as well, at some cost.
       const double whole = (double)(t / sms), frac = (double)(t % sms) / (double)sms;
@@ -152,27 +153,49 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
       if (rounds * (double)per_tile < best) { best = rounds * (double)per_tile; BT = cand; }
     }
   }
-  u.BT = BT; u.NACC = (BT > (atm ? 192u : 256u)) ? 1u : 2u;
-  // accumulators per tile: as many as the accumulator columns hold (192 per buffer with the operand in tensor memory, 256
-  // without).  96 < BT <= 192 gives up the second buffer for a second accumulator when the k loop is long enough to pay
-  // for the exposed epilogue.
-  const uint32_t acc_cols = atm ? 192u : 256u;
-  u.KSPLIT = BT * 4u <= acc_cols ? 4u : BT * 2u <= acc_cols ? 2u : 1u;
-  if (atm && u.KSPLIT == 1u && BT <= acc_cols && KSn >= 24u) { u.KSPLIT = 2u; u.NACC = 1u; }      // (depends on K and the tile only: conv3 chunks and the whole clip agree)
+  // ---- tensor memory (512 columns).  fp16 weights: two accumulator buffers of 256 columns.  Quantised weights: the accumulators
+  // first, the dequantised operand's stages in all the columns behind them.  Two accumulator buffers (the next tile's multiplies
+  // overlap the epilogue) for tiles up to 128 tokens, one beyond.  Every hand-over between the roles is a round trip of several
+  // hundred cycles, so the number of operand stages in flight, not the conversion or the multiplies, is what bounds narrow and
+  // medium tiles: they get every column the accumulators leave.  (Consecutive multiplies into one accumulator issue back to back
+  // at the tensor pipe's rate, so a tile has ONE accumulator: KSPLIT stays 1.)
+  u.BT = BT; u.KSPLIT = 1u;
+  u.NACC = atm ? (BT <= 128u ? 2u : 1u) : (BT > 256u ? 1u : 2u);
   // pipeline step: 128 k for quantised weights up to 256 tokens (the hand-over costs dominate there), 64 k otherwise (wide tiles
   // are bound by the multiplies and their stages are large; fp16 weights are bound by shared memory).  Depends on the tile only.
   u.KW = (atm && BT <= 256u) ? 2u : 1u;
+#ifdef P0P_KNOBS
+  if (const char* e = getenv("P0P_NACC")) u.NACC = (uint32_t)atoi(e);
+  if (const char* e = getenv("P0P_KW")) u.KW = (uint32_t)atoi(e);
+#endif
+  u.acc_stride = atm ? BT : 256u;
+  u.a_col0 = atm ? ((u.NACC * BT + 31u) & ~31u) : 512u;
   // Token-ring stages: what shared memory allows for wide tiles; more for narrow ones, whose loads would otherwise be exposed.
-  // Operand stages: tensor memory holds four 32-column sub-stages.  Tiles above 128 tokens (bound by the multiplies): both rings
-  // in lock step on shared barriers.  fp16 weights have no operand ring of their own: the weight tile travels with the tokens.
+  // fp16 weights have no operand ring of their own: the weight tile travels with the tokens (lock step, shared barriers).
   if (!atm) { u.NS = BT > 192u ? 3u : 4u; u.NA = u.NS; u.LOCK = 1u; }
-  else if (BT > 256u) { u.NS = 3u; u.NA = 3u; u.LOCK = 1u; }
-  else if (BT > 128u) { u.NS = 2u; u.NA = 2u; u.LOCK = 1u; }
-  else { u.NS = BT > 64u ? 4u : BT > 32u ? 6u : 8u; u.NA = 2u; u.LOCK = 0u; }
+  else {
+    u.NA = std::min<uint32_t>(U_NA_MAX, (512u - u.a_col0) / (32u * u.KW));
+    const uint32_t xstage = u.KW * BT * 128u;
+    u.NS = std::max(2u, std::min<uint32_t>(U_NX_MAX, (144u * 1024u) / xstage));
+    u.LOCK = 0u;
+    // Tiles above 128 tokens are bound by the multiplies, and there every instruction the issuing warp runs between two
+    // multiplies shows: the two rings advance in lock step on shared barriers (one wait, one commit per step).
+    if (u.KW == 1u || BT > 128u) { u.NS = std::min(u.NS, u.NA); u.NA = u.NS; u.LOCK = 1u; }
+  }
+#ifdef P0P_KNOBS
+  if (const char* e = getenv("P0P_NS")) u.NS = (uint32_t)atoi(e);
+  if (const char* e = getenv("P0P_NA")) u.NA = (uint32_t)atoi(e);
+  if (const char* e = getenv("P0P_LOCK")) u.LOCK = (uint32_t)atoi(e);
+  if (u.LOCK) u.NA = u.NS = std::min(u.NS, u.NA);
+#endif
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
   const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
   const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * u.KW * BT * 128u + (size_t)U_EPI_BYTES + 1024u;
-  u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (100 * 1024 + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
+  size_t q_cap = 100 * 1024;
+#ifdef P0P_KNOBS
+  if (const char* e = getenv("P0P_QCAP")) q_cap = (size_t)atoi(e) * 1024;
+#endif
+  u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (q_cap + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
   if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
   u.m_tiles = (p.M + BT - 1u) / BT;
   // ---- split-K: when the tiles leave SMs idle (few output columns) or the last round is nearly empty, each tile's k loop
