@@ -6,6 +6,7 @@
 // One block = two tiles of 128 queries of one head that share every K / V tile (or one tile: see attn_plan).  Tensor memory (512 columns x 128 lanes):
 // S of tile A | S of tile B | O of tile A | O of tile B, 128 fp32 columns each; lane = query row.  P (fp16, two keys per
 // column) is written over the first 64 columns of its S, which is free once the softmax threads hold the row.
+// P is handed over in two halves of 64 keys, so the first half of PV runs under the second half's exponentials.
 // Roles: warp 0 loads tiles by tensor-map copies into a ring of 32-KB slots (K0 V0 K1 V1 ...); warp 1 issues the
 // multiplies in the order  PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1), so that while the softmax of one tile runs the tensor
 // cores work on the other; warps 2-5 are the softmax of tile A, warps 6-9 of tile B: one thread per query row, the whole
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
   unsigned char* gbase = atc_raw + (base - smem_u32(atc_raw));
   const uint32_t q_sm = base, kv_sm = base + 2u * ATC_TILE, bars = kv_sm + ATC_SLOTS * ATC_TILE;
   const uint32_t q_full = bars, kv_full = bars + 8u, kv_empty = kv_full + 8u * ATC_SLOTS, s_full = kv_empty + 8u * ATC_SLOTS;
-  const uint32_t p_full = s_full + 16u, o_full = p_full + 16u, tmem_slot = o_full + 16u;
+  const uint32_t p_full = s_full + 16u, o_full = p_full + 32u, tmem_slot = o_full + 16u;      // p_full: [tile][half of the keys]
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   // the grid: first every head's two-tile blocks, then every head's one-tile blocks (the short ones fill the last wave)
   const bool hasB = blockIdx.x < p.Hq * p.np;
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
   if (tid == 0) {
     mbar_init(q_full, 1u);
     for (uint32_t s = 0; s < ATC_SLOTS; s++) { mbar_init(kv_full + 8u * s, 1u); mbar_init(kv_empty + 8u * s, 1u); }
-    for (uint32_t t = 0; t < 2u; t++) { mbar_init(s_full + 8u * t, 1u); mbar_init(p_full + 8u * t, 4u); mbar_init(o_full + 8u * t, 1u); }
+    for (uint32_t t = 0; t < 2u; t++) { mbar_init(s_full + 8u * t, 1u); mbar_init(p_full + 16u * t, 4u); mbar_init(p_full + 16u * t + 8u, 4u); mbar_init(o_full + 8u * t, 1u); }
     fence_mbar_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512u); tmem_relinquish(); }
@@ -131,13 +132,21 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
       if (!__all_sync(0xffffffffu, rdy)) { ok = false; break; }
       const uint64_t vd = umma_desc_sw128(kv_sm + sv * ATC_TILE), kd = umma_desc_sw128(kv_sm + sk * ATC_TILE);
       for (uint32_t t = 0; t < nt; t++) {
-        if (!__all_sync(0xffffffffu, mbar_wait(p_full + 8u * t, j & 1u, p.status, 406))) { ok = false; break; }
+        // P arrives in two halves of 64 keys: the first four multiplies of PV run while the second half's exponentials are computed
+        if (!__all_sync(0xffffffffu, mbar_wait(p_full + 16u * t, j & 1u, p.status, 406))) { ok = false; break; }
         tc_fence_after();
         const uint32_t s_col = tmem_base + t * 128u, o_col = tmem_base + 256u + t * 128u;
         const uint64_t qdt = qd[t];
         if (elect_one()) {
 #pragma unroll
-          for (uint32_t kk = 0; kk < 8u; kk++) umma_f16_ts(o_col, s_col + 8u * kk, vd + (kk >> 2) * 1024u + 2u * (kk & 3u), idesc, j | kk);
+          for (uint32_t kk = 0; kk < 4u; kk++) umma_f16_ts(o_col, s_col + 8u * kk, vd + 2u * kk, idesc, j | kk);
+        }
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, mbar_wait(p_full + 16u * t + 8u, j & 1u, p.status, 409))) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (uint32_t kk = 4u; kk < 8u; kk++) umma_f16_ts(o_col, s_col + 8u * kk, vd + 1024u + 2u * (kk & 3u), idesc, 1u);
           if (more) {
 #pragma unroll
             for (uint32_t kk = 0; kk < 8u; kk++) umma_f16_ss(s_col, qdt + (kk >> 2) * 1024u + 2u * (kk & 3u), kd + (kk >> 2) * 1024u + 2u * (kk & 3u), idesc, kk);
@@ -217,12 +226,14 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) k_attn_tc(const AttnTcP p, con
             pk[e] = *reinterpret_cast<const uint32_t*>(&hp);
           }
           tmem_st16(s_addr + 16u * c, pk);
+          if (c == 1 || c == 3) {                                   // a half of P (64 keys) is complete: hand it to the multiplies
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 16u * t + (c == 3 ? 8u : 0u));
+          }
         }
         l += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + 8u * t);
       }
       // ---- O / l -> global, token-major, head h at column h * 128
       if (ok && mbar_wait(o_full + 8u * t, 0u, p.status, 408)) {
