@@ -66,6 +66,7 @@ uint64_t plan_decode(DecodeP& d, DecodeLaunch& L, int sms, size_t smem_per_sm) {
   L.grid = (int)std::min<uint64_t>(d.T / (d.KC / (uint32_t)D_STAGE_K), (uint64_t)per_sm * (uint64_t)sms);
   while ((uint64_t)d.T * (uint64_t)L.grid >= (1ull << 32)) L.grid = (L.grid + 1) / 2;      // the kernels' range arithmetic is 32-bit
   d.G = (uint32_t)L.grid;
+  d.whole = (p.K % d.KC == 0u && d.units >= 4u * d.G) ? 1u : 0u;
   L.fin_blocks = (p.epi == P0P_EPI_HEADS || p.epi == P0P_EPI_ONORMGATE) ? (p.N + 127u) / 128u : (((p.N + 3u) & ~3u) + 127u) / 128u;
   return 2ull * d.S * p.M * d.nslots * 4ull;
 }

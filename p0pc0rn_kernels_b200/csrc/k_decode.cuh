@@ -54,6 +54,8 @@ struct DecodeP {
   uint32_t units;     // tiles * S
   uint32_t nslots;    // tiles * 64
   uint32_t T, G;      // stages of the whole call (tiles * K / 256) and blocks of the stream kernel: block b takes stages [b*T/G, (b+1)*T/G)
+  uint32_t whole;     // 1: the ranges are rounded to whole units instead (many units per block: the even split gains nothing there
+                      // and costs a partial unit per block)
   float* scratch;     // [S][2 parts][M][nslots] fp32
   int* status;
   uint32_t vec32;     // fp32 tokens and the prologue vector may be read with 16-byte loads
@@ -77,9 +79,12 @@ __device__ __forceinline__ DSeg d_seg(const DecodeP& d, uint32_t i) {
   return g;
 }
 // (T * G stays below 2^32: the plan sees to it, so that these divisions are 32-bit ones — the second stage does two per k-block)
-__device__ __forceinline__ uint32_t d_range(const DecodeP& d, uint32_t b) { return (b * d.T) / d.G; }
+__device__ __forceinline__ uint32_t d_range(const DecodeP& d, uint32_t b) {
+  return d.whole ? ((b * d.units) / d.G) * (d.KC / (uint32_t)D_STAGE_K) : (b * d.T) / d.G;
+}
 // does a block boundary fall strictly inside the unit that spans stages [u0, u0 + n)?  (then the unit has a part 1)
 __device__ __forceinline__ bool d_unit_split(const DecodeP& d, uint32_t u0, uint32_t n) {
+  if (d.whole) return false;
   const uint32_t b = ((u0 + 1u) * d.G + d.T - 1u) / d.T;                         // the first boundary above u0
   return b < d.G && d_range(d, b) < u0 + n;
 }
