@@ -462,8 +462,8 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
         """every rank's columns are in every copy once all ranks are past this point of their streams"""
         if fused: gpu.peerBarrier(flags, flag_peers, rank, world, BARRIER_CYCLES)
 
-    def block(M, i, gather=True):
-        """one pass of the MLP block over M tokens with weight copy i"""
+    def block(M, i, gather=True, xb=xb):
+        """one pass of the MLP block over M tokens with weight copy i (xb: the residual stream it updates in place)"""
         P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
         yh = {"buf": hf, "ld": FF, "n0": rank * ffl, "peers": hf_peers} if fused else {"buf": hl, "ld": ffl}
         a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
@@ -587,7 +587,64 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_ms = float(t.item())
     h2d = M * HID * 4
-    e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms}
+    e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms,
+           "pipeline": "none: upload, block, read-back one after the other on one stream"}
+    # ---- N = 1: the same steps as a serving loop would run them: three contexts of the library on three streams (upload / block /
+    # read-back) over a ring of three residual buffers, so that step i's block runs while step i + 1's tokens arrive and step
+    # i - 1's result leaves.  Every step still makes its own host -> device copy from page-locked memory and its own device ->
+    # host read through the public API, inside the timed region.  (N > 1 keeps the plain loop: the peers' copies of the residual
+    # are fixed buffers.)
+    if world == 1:
+        NB = 3
+        s_up, s_dn = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        g_up = P.createGpu({"device": local, "stream": s_up.cuda_stream}); g_dn = P.createGpu({"device": local, "stream": s_dn.cuda_stream})
+        xbs = [gpu.buffer(M * HID * 4, f"residual.{b}") for b in range(NB)]
+        up_view = [g_up.wrap(b.ptr, M * HID * 4) for b in xbs]; dn_view = [g_dn.wrap(b.ptr, M * HID * 4) for b in xbs]
+        hu = C.c_void_p(); g_up._check(lib.p0p_host_alloc(g_up._h, M * HID * 4, C.byref(hu)))
+        pin_up = np.ctypeslib.as_array(C.cast(hu, C.POINTER(C.c_float)), shape=(M * HID,)); pin_up[:] = x_host[: M * HID]
+        pin_dn = []
+        for b in range(NB):
+            hd = C.c_void_p(); g_dn._check(lib.p0p_host_alloc(g_dn._h, out_bytes, C.byref(hd)))
+            pin_dn.append(np.ctypeslib.as_array(C.cast(hd, C.POINTER(C.c_uint8)), shape=(out_bytes,)))
+        graphs = {}
+        for b in range(NB):
+            for i in range(args.copies):
+                block(M, i, True, xbs[b]); torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream): block(M, i, True, xbs[b])
+                graphs[(b, i)] = g
+        ev_up = [torch.cuda.Event() for _ in range(NB)]; ev_c = [torch.cuda.Event() for _ in range(NB)]; ev_dn = [torch.cuda.Event() for _ in range(NB)]
+
+        def enqueue(sidx):
+            b = sidx % NB
+            s_up.wait_event(ev_dn[b])                                    # the buffer's previous result has left
+            g_up.upload(pin_up, "", up_view[b], 0); ev_up[b].record(s_up)
+            stream.wait_event(ev_up[b]); graphs[(b, sidx % args.copies)].replay(); ev_c[b].record(stream)
+
+        def collect(sidx):
+            b = sidx % NB
+            s_dn.wait_event(ev_c[b])
+            g_dn.read(dn_view[b], 0, out_bytes, out=pin_dn[b]); ev_dn[b].record(s_dn)
+
+        def pipelined(n):
+            for sidx in range(n):
+                enqueue(sidx)
+                if sidx >= NB - 1: collect(sidx - (NB - 1))
+            for sidx in range(max(0, n - (NB - 1)), n): collect(sidx)
+
+        pipelined(6); torch.cuda.synchronize()
+        n_p = max(10, min(args.steps, 60))
+        t0 = time.perf_counter(); pipelined(n_p); torch.cuda.synchronize()
+        p_ms = (time.perf_counter() - t0) / n_p * 1e3
+        # the pipelined result is the plain loop's: same tokens in, same bits out
+        same = bool(np.array_equal(pin_dn[(n_p - 1) % NB], pin_out))
+        e2e = {"value": block_flops(M) / (p_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": p_ms,
+               "pipeline": "3 streams (upload / block / read-back) over a ring of 3 residual buffers; every step copies its tokens in and its result out",
+               "unpipelined": {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "ms_per_step": e2e_ms}, "matches_unpipelined_bits": same}
+        for v in up_view: g_up.free(v)
+        for v in dn_view: g_dn.free(v)
+        del graphs
+        for b in xbs: gpu.free(b)
 
     # ---- N > 1: one more block from the same tokens, checked.  Every rank's copy of the hidden row and of the residual must
     # hold the same bits (each rank wrote its columns into all copies): element-wise MAX and MIN over the ranks agree.  Rank 0
