@@ -6,8 +6,9 @@
 One step = one pass of the block over M tokens (default 512): row statistics, the fused gate/up GEMM, the fused
 down GEMM.  `value` is TFLOP/s (2*M*N*K of both GEMMs over the device time of K steps, inputs resident in HBM);
 `e2e` is the same through the public API with HOST buffers (page-locked host -> device copy of the tokens and a
-device -> host read of the result inside the timed region).  Decode-sized M (1, 16) is measured next to it and
-reported as GB/s of the weight stream in `cases`.
+device -> host read of the result inside the timed region; at N = 1 the steps run as a three-stream pipeline - upload,
+block, read-back over a ring of residual buffers - and the plain one-after-the-other loop is reported beside it).
+Decode-sized M (1, 16) is measured next to it and reported as GB/s of the weight stream in `cases`.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m 512]
 

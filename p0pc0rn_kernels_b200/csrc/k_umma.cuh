@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   if (tid == 0) {
     for (uint32_t s = 0; s < U_NX_MAX; s++) { mbar_init(xfull + 8u * s, 1u); mbar_init(xempty + 8u * s, 1u); }      // the producer's expect_tx arrival / the multiplies' commit
-    for (uint32_t s = 0; s < U_NA_MAX; s++) { mbar_init(afull + 8u * s, (ATM ? 4u * KW : 0u) + (lock ? 1u : 0u)); mbar_init(aempty + 8u * s, 1u); }       // the dequantisation warps of a step (+ the token producer) / the commit
+    for (uint32_t s = 0; s < U_NA_MAX; s++) { mbar_init(afull + 8u * s, (ATM ? (KW == 2u && lock ? 8u : 4u) : 0u) + (lock ? 1u : 0u)); mbar_init(aempty + 8u * s, 1u); }       // the dequantisation warps of a step (+ the token producer) / the commit
     for (uint32_t s = 0; s < (uint32_t)U_NQ_MAX; s++) { mbar_init(wq_full + 8u * s, 1u); mbar_init(wq_empty + 8u * s, U_DEQ_WARPS); }
     for (uint32_t b = 0; b < 2u; b++) { mbar_init(acc_full + 8u * b, 1u); mbar_init(acc_empty + 8u * b, 4u); }
     fence_mbar_init();
@@ -359,57 +359,78 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     const uint32_t rec_row = tile_off + (ENC == P0P_ENC_Q4 ? rr * 16u : rr * 64u);
     const uint32_t rec_sm = tile_off + (ENC == P0P_ENC_Q4 ? 1024u + rr * 4u : 4096u + rr * 2u);
     const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + u.a_col0;
-    const uint32_t sub = KW == 2u ? grp : 0u, stride = KW == 2u ? 1u : 2u;
-    // this group's steps are every `stride`-th of the running count of steps; their operand stage walks the ring of NA with them
-    uint32_t as = KW == 2u ? 0u : grp, aph = 0u;
+    // How the two groups share the steps.  Steps of 64 k, and steps of 128 k with rings of their own (narrow tiles): the groups
+    // take whole steps in turn, so a warp pays its trip round this loop - a few hundred cycles of serial latency whatever the work -
+    // once per step it converts, and with three or more operand stages neither group waits for the multiplies of its own last
+    // step.  Steps of 128 k in lock step (two stages only): group g converts sub-step g of every step, both side by side.
+    constexpr bool ALT = KW == 1u || !lock;
+    const uint32_t stride = ALT ? 2u : 1u;
+    uint32_t as = ALT ? grp : 0u, aph = 0u;
     Ring qr(NQ);
-    uint32_t gpar = 0;                                             // parity of the count of steps before this record stage (KW = 1)
+    uint32_t gpar = 0;                                             // parity of the count of steps before this record stage (ALT)
     bool ok = true;
+    // one operand row of k-step jj of the record stage -> 32 columns of tensor memory at ta
+    auto convert = [&](uint32_t jj, uint32_t ta) {
+      const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + jj * UQ<ENC>::RB;
+      if (ENC == P0P_ENC_Q4) {
+        // both 32-k halves of the row are fetched first, so that the second half's loads are in flight while the first converts
+        const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 1280u);
+        const uint32_t sm0 = u_lds32(rec + rec_sm), sm1 = u_lds32(rec + rec_sm + 1280u);
+        const uint32_t w0[4] = {c0.x, c0.y, c0.z, c0.w}, w1[4] = {c1.x, c1.y, c1.z, c1.w};
+        __half2 v[16];
+        q4_row32(w0, sm0, v);
+        tmem_st16(ta, *reinterpret_cast<const uint32_t(*)[16]>(v));
+        q4_row32(w1, sm1, v);
+        tmem_st16(ta + 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
+      } else {
+        const uint32_t sb = u_lds16(rec + rec_sm);
+#pragma unroll
+        for (uint32_t h = 0; h < 2u; h++) {
+          const uint4 c0 = u_lds128(rec + rec_row + h * 32u), c1 = u_lds128(rec + rec_row + h * 32u + 16u);
+          const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          __half2 v[16];
+          q8_row<8>(w, sb, v);
+          tmem_st16(ta + h * 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
+        }
+      }
+    };
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
       const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t n = un.ke - un.kb;
       for (uint32_t j0 = 0; j0 < n && ok; j0 += UQ<ENC>::KSUP, qr.next()) {
         const uint32_t cnt = min(UQ<ENC>::KSUP, n - j0);
         bool fresh = true;                                         // the record stage is awaited at this group's first k-step in it
-        // k-step jj of the record stage is this group's when jj % 2 == grp (KW = 2: sub-step grp of a step) or when the running
-        // count of k-steps has the group's parity (KW = 1).  KW = 2 with an odd tail: group 1 passes the missing sub-step once,
-        // only to arrive (after the same wait for the free stage as any arrival).
-        const uint32_t jfirst = KW == 2u ? grp : (grp ^ gpar);
-        const uint32_t jend = cnt + (KW == 2u ? (grp & cnt & 1u) : 0u);
-        for (uint32_t jj = jfirst; jj < jend; jj += 2u) {
-          const bool have = jj < cnt;
-          if ((have && fresh && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(aempty + 8u * as, aph ^ 1u, u.status, 208)) { ok = false; break; }
-          if (have) {
+        if (ALT) {
+          // the stage's steps (KW k-steps each, the last may be short); this group's are those of its parity in the running count
+          const uint32_t nst = (cnt + KW - 1u) / KW;
+          for (uint32_t st = grp ^ gpar; st < nst; st += 2u) {
+            if ((fresh && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(aempty + 8u * as, aph ^ 1u, u.status, 208)) { ok = false; break; }
             fresh = false;
-            const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + jj * UQ<ENC>::RB;
-            const uint32_t ta = ta0 + (as * KW + sub) * 32u;
-            if (ENC == P0P_ENC_Q4) {
-              // both 32-k halves of the row are fetched first, so that the second half's loads are in flight while the first converts
-              const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 1280u);
-              const uint32_t sm0 = u_lds32(rec + rec_sm), sm1 = u_lds32(rec + rec_sm + 1280u);
-              const uint32_t w0[4] = {c0.x, c0.y, c0.z, c0.w}, w1[4] = {c1.x, c1.y, c1.z, c1.w};
-              __half2 v[16];
-              q4_row32(w0, sm0, v);
-              tmem_st16(ta, *reinterpret_cast<const uint32_t(*)[16]>(v));
-              q4_row32(w1, sm1, v);
-              tmem_st16(ta + 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
-            } else {
-              const uint32_t sb = u_lds16(rec + rec_sm);
 #pragma unroll
-              for (uint32_t h = 0; h < 2u; h++) {
-                const uint4 c0 = u_lds128(rec + rec_row + h * 32u), c1 = u_lds128(rec + rec_row + h * 32u + 16u);
-                const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-                __half2 v[16];
-                q8_row<8>(w, sb, v);
-                tmem_st16(ta + h * 16u, *reinterpret_cast<const uint32_t(*)[16]>(v));
-              }
-            }
+            for (uint32_t sub = 0; sub < KW; sub++)
+              if (st * KW + sub < cnt) convert(st * KW + sub, ta0 + (as * KW + sub) * 32u);
             tmem_st_wait(); tc_fence_before();                      // tensor-memory stores done and ordered before the MMA warp's read
+            __syncwarp();
+            if (lane == 0) mbar_arrive(afull + 8u * as);
+            as += stride; if (as >= NA) { as -= NA; aph ^= 1u; }
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(afull + 8u * as);
-          as += stride; if (as >= NA) { as -= NA; aph ^= 1u; }
+          gpar ^= nst & 1u;
+        } else {
+          // k-step jj of the record stage is this group's when jj % 2 == grp (sub-step grp of a step).  An odd tail: group 1 passes
+          // the missing sub-step once, only to arrive (after the same wait for the free stage as any arrival).
+          const uint32_t jend = cnt + (grp & cnt & 1u);
+          for (uint32_t jj = grp; jj < jend; jj += 2u) {
+            const bool have = jj < cnt;
+            if ((have && fresh && !mbar_wait(wq_full + 8u * qr.s, qr.ph, u.status, 207)) || !mbar_wait(aempty + 8u * as, aph ^ 1u, u.status, 208)) { ok = false; break; }
+            if (have) {
+              fresh = false;
+              convert(jj, ta0 + (as * KW + grp) * 32u);
+              tmem_st_wait(); tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(afull + 8u * as);
+            as += stride; if (as >= NA) { as -= NA; aph ^= 1u; }
+          }
         }
-        gpar ^= cnt & 1u;
         // Every warp releases every record stage once, after its last k-step there.  A group with no k-step of its own in the
         // stage still waits for the stage to be filled first: its release must not land in the barrier phase of the stage's
         // previous contents.
