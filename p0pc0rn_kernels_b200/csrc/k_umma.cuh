@@ -15,8 +15,8 @@
 //                              the unit's last step it commits to the accumulator's "full" barrier
 //   warps 2..5      epilogue   tcgen05.ld of 16 tokens at a time, fused epilogue (or the raw partial sums of a split-K
 //                              unit), row-wise 16-byte stores
-//   warps 6..13     dequant    eight warps share every k-step: a thread converts 32 k of one weight row (warp % 4 picks the
-//                              32 rows a warp may reach in tensor memory, warp / 4 the half of the step): codes -> fp16 tile
+//   warps 6..13     dequant    two groups of four warps; a thread converts whole operand rows of 64 k (warp % 4 picks the 32 rows
+//                              a warp may reach in tensor memory, warp / 4 the group): codes -> fp16 tile
 //                              values f16(q*s+mn) / f16(q*s), bit-exact (packed HFMA2 path; a row whose scale / minimum fail the
 //                              exactness test is redone in fp32 by its own lane), written straight into tensor memory
 //                              (tcgen05.st): the multiply takes A from there
@@ -138,9 +138,10 @@ constexpr uint32_t U_NX_MAX = 8;         // most stages of the token ring
 // are bound by the hand-overs instead; their token tiles are small, so the X ring gets its own barriers and more stages than
 // tensor memory has operand stages (the load of a tile is only issued once its stage is free, and with few stages that round
 // trip would be exposed).
-// Dequantisation: two groups of four warps; a thread converts one whole operand row (64 k).  KW = 1: the groups take the steps in
-// turn.  KW = 2: group g converts sub-step g of every step, so both groups fill the same stage side by side.  The warps that
-// wait are parked by the hardware (mbar_try), not spinning beside the ones that work.
+// Dequantisation: two groups of four warps; a thread converts one whole operand row (64 k) per k-step.  The groups take the steps
+// in turn (each step's one or two k-steps by one group), except in the lock-step 128-k variant, whose two operand stages
+// leave no room for that: there group g converts sub-step g of every step, both side by side.  The warps that wait are
+// parked by the hardware (mbar_try), not spinning beside the ones that work.
 // KW and LOCK are compile-time (three variants exist: (1, lock), (2, lock), (2, separate)): the issuing warp's loop is the
 // critical path of wide tiles and must not carry run-time choices.
 template <int ENC, int EPI, int KW_, bool LOCK_>
