@@ -58,7 +58,7 @@ struct UmmaP {
   uint32_t NACC;        // accumulators: 2 (the next tile's multiply overlaps the epilogue) or 1 (wide tiles: tensor memory holds one)
   uint32_t KSPLIT;      // accumulators per tile that take the 16-k multiplies in turn (1, 2 or 4), summed by the epilogue
   uint32_t NS;          // stages of the token ring (2 .. 8)
-  uint32_t KW;          // k-steps of 64 k per pipeline step (1 or 2)
+  uint32_t KW;          // k-steps of 64 k per pipeline step (1, 2 or 4)
   uint32_t NA;          // stages of the dequantised operand in tensor memory (a_col0 + NA * KW * 32 <= 512, NA <= 8); fp16 weights: = NS
   uint32_t acc_stride;  // tensor-memory columns from one accumulator buffer to the next
   uint32_t a_col0;      // first tensor-memory column of the operand stages (quantised weights): the accumulators end there

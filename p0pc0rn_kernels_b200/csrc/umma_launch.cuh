@@ -161,9 +161,43 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // at the tensor pipe's rate, so a tile has ONE accumulator: KSPLIT stays 1.)
   u.BT = BT; u.KSPLIT = 1u;
   u.NACC = atm ? (BT <= 128u ? 2u : 1u) : (BT > 256u ? 1u : 2u);
+  u.m_tiles = (p.M + BT - 1u) / BT;
+  // ---- split-K: when the tiles leave SMs idle (few output columns) or the last round is nearly empty, each tile's k loop
+  // is cut into S units whose fp32 partial sums a second kernel adds.  Never for conv3 (S would depend on M, and chunked
+  // and whole-clip calls must add in the same order).
+  const uint32_t tiles_all = u.n_tiles * u.m_tiles;
+  u.S = 1u; u.ks_per = KSn; u.T0 = tiles_all;
+  if (p.xmode != P0P_X_CONV3) {
+    const uint64_t tiles = tiles_all;
+    const uint64_t kstep = std::max<uint64_t>(5u * BT / 2u, 750u), epi = 24u * BT;
+    const uint64_t whole = KSn * kstep + (u.NACC == 1u ? epi : 0u);                  // one unsplit tile
+    uint64_t best = ((tiles + sms - 1) / sms) * whole;
+    // (a) every tile split (few tiles)
+    for (uint32_t S = 2u; S <= 16u; S++) {
+      const uint32_t per = (KSn + S - 1u) / S;
+      if (per < 8u || (uint64_t)(S - 1u) * per >= KSn) continue;                     // every unit gets k-steps, at least 8 each
+      const uint64_t cost = ((tiles * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u + (uint64_t)S * BT * 40u;   // + pipeline fill per unit; second kernel: launch, partials written and read
+      if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = 0u; }
+    }
+    // (b) only the tiles of the last round split over the SMs that round would leave idle
+    const uint64_t t0 = (tiles / sms) * sms, tail = tiles - t0;
+    if (t0 && tail) {
+      for (uint32_t S = 2u; S <= 16u; S++) {
+        const uint32_t per = (KSn + S - 1u) / S;
+        if (per < 4u || (uint64_t)(S - 1u) * per >= KSn) continue;
+        const uint64_t cost = (t0 / sms) * whole + ((tail * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u;
+        if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = (uint32_t)t0; }
+      }
+    }
+  }
   // pipeline step: 128 k for quantised weights up to 256 tokens (the hand-over costs dominate there), 64 k otherwise (wide tiles
   // are bound by the multiplies and their stages are large; fp16 weights are bound by shared memory).  Depends on the tile only.
   u.KW = (atm && BT <= 256u) ? 2u : 1u;
+  // 256 k for 4-bit weights on tiles up to 128 tokens: there each role's loop, not its work, is what a step costs (a record stage
+  // of 4-bit weights is 256 k long; 8-bit stages are 128 k, so those keep 128-k steps).  Three operand stages of 128 columns
+  // must fit behind the accumulators: one accumulator buffer above 64 tokens.  Not for units of few k-steps (split-K of a small
+  // weight): two or three such steps would be all fill and drain.
+  if (p.enc == P0P_ENC_Q4 && BT <= 128u && u.ks_per >= 32u) { u.KW = 4u; if (BT > 64u) u.NACC = 1u; }
 #ifdef P0P_KNOBS
   if (const char* e = getenv("P0P_NACC")) u.NACC = (uint32_t)atoi(e);
   if (const char* e = getenv("P0P_KW")) u.KW = (uint32_t)atoi(e);
@@ -197,35 +231,6 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
 #endif
   u.NQ = qstage ? (uint32_t)std::min<size_t>(std::min<size_t>(U_NQ_MAX, (q_cap + qstage - 1) / qstage), (227 * 1024 - fixed) / qstage) : 0u;
   if (qstage && u.NQ < 2u) return fail(c, -12, "gemm: no room for the record stages of this tile shape");
-  u.m_tiles = (p.M + BT - 1u) / BT;
-  // ---- split-K: when the tiles leave SMs idle (few output columns) or the last round is nearly empty, each tile's k loop
-  // is cut into S units whose fp32 partial sums a second kernel adds.  Never for conv3 (S would depend on M, and chunked
-  // and whole-clip calls must add in the same order).
-  const uint32_t tiles_all = u.n_tiles * u.m_tiles;
-  u.S = 1u; u.ks_per = KSn; u.T0 = tiles_all;
-  if (p.xmode != P0P_X_CONV3) {
-    const uint64_t tiles = tiles_all;
-    const uint64_t kstep = std::max<uint64_t>(5u * BT / 2u, 750u), epi = 24u * BT;
-    const uint64_t whole = KSn * kstep + (u.NACC == 1u ? epi : 0u);                  // one unsplit tile
-    uint64_t best = ((tiles + sms - 1) / sms) * whole;
-    // (a) every tile split (few tiles)
-    for (uint32_t S = 2u; S <= 16u; S++) {
-      const uint32_t per = (KSn + S - 1u) / S;
-      if (per < 8u || (uint64_t)(S - 1u) * per >= KSn) continue;                     // every unit gets k-steps, at least 8 each
-      const uint64_t cost = ((tiles * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u + (uint64_t)S * BT * 40u;   // + pipeline fill per unit; second kernel: launch, partials written and read
-      if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = 0u; }
-    }
-    // (b) only the tiles of the last round split over the SMs that round would leave idle
-    const uint64_t t0 = (tiles / sms) * sms, tail = tiles - t0;
-    if (t0 && tail) {
-      for (uint32_t S = 2u; S <= 16u; S++) {
-        const uint32_t per = (KSn + S - 1u) / S;
-        if (per < 4u || (uint64_t)(S - 1u) * per >= KSn) continue;
-        const uint64_t cost = (t0 / sms) * whole + ((tail * S + sms - 1) / sms) * (per * kstep + epi + 3000u) + 6000u;
-        if (cost * 20u < best * 19u) { best = cost; u.S = S; u.ks_per = per; u.T0 = (uint32_t)t0; }
-      }
-    }
-  }
   const uint64_t sk_bytes = u.S > 1u ? (uint64_t)u.S * (tiles_all - u.T0) * BT * 128u * 4u : 0u;
   if (pro_bytes + sk_bytes) {
     if (int r = ensure_scratch(c, pro_bytes + sk_bytes + 256)) return r;
@@ -268,10 +273,10 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   const int grid = (int)std::min<uint64_t>((uint64_t)u.T0 + (uint64_t)(tiles_all - u.T0) * u.S, sms);
   const int smem_max = 227 * 1024;          // the most dynamic shared memory a block may opt into on sm_100
   if (smem > (size_t)smem_max) return fail(c, -12, "gemm: tile configuration needs %zu bytes of shared memory", smem);
-  const uint32_t variant = u.KW == 1u ? 0u : u.LOCK ? 1u : 2u;
+  const uint32_t variant = u.KW == 1u ? 0u : u.KW == 4u ? 3u : u.LOCK ? 1u : 2u;
   const umma_kernel_fn kern = p.enc == P0P_ENC_Q4 ? umma_kernel_q4(variant, p.epi) : p.enc == P0P_ENC_Q8 ? umma_kernel_q8(variant, p.epi) : umma_kernel_f16(p.epi);
   // the shared-memory ceiling is an attribute of (kernel, device): raised once for each pair
-  static DeviceOnce once[3][3][7];
+  static DeviceOnce once[3][4][7];
   cudaError_t e = cudaSuccess;
   if (once[p.enc][variant][p.epi].run(c->device, [&] { e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max); return (int)e; }))
     return cuda_fail(c, e != cudaSuccess ? e : cudaErrorInvalidDevice, "tensor-core kernel attribute");
