@@ -125,7 +125,7 @@ struct Ring {
 constexpr uint32_t U_NA_MAX = 8;         // most operand stages in tensor memory
 constexpr uint32_t U_DEQ_WARPS = 8;      // two groups of four
 constexpr uint32_t U_NX_MAX = 8;         // most stages of the token ring
-// Pipeline steps.  One step covers KW k-steps of 64 k (KW = 1 or 2, chosen per launch): every hand-over between the roles - a
+// Pipeline steps.  One step covers KW k-steps of 64 k (KW = 1, 2 or 4, chosen per launch): every hand-over between the roles - a
 // barrier wait, a fence, a commit, a trip round a warp's loop - costs a few hundred cycles of single-warp latency, which for
 // narrow and medium tiles is more than the multiplies of 64 k take, so those tiles move 128 k per hand-over.
 // Three producers feed the multiply, each through a ring of stages with a "ready" and a "free" mbarrier per stage:
@@ -142,7 +142,7 @@ constexpr uint32_t U_NX_MAX = 8;         // most stages of the token ring
 // in turn (each step's one or two k-steps by one group), except in the lock-step 128-k variant, whose two operand stages
 // leave no room for that: there group g converts sub-step g of every step, both side by side.  The warps that wait are
 // parked by the hardware (mbar_try), not spinning beside the ones that work.
-// KW and LOCK are compile-time (three variants exist: (1, lock), (2, lock), (2, separate)): the issuing warp's loop is the
+// KW and LOCK are compile-time (four variants exist: (1, lock), (2, lock), (2, separate), (4, separate; 4-bit weights)): the issuing warp's loop is the
 // critical path of wide tiles and must not carry run-time choices.
 template <int ENC, int EPI, int KW_, bool LOCK_>
 __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW) {
