@@ -149,6 +149,10 @@ int p0p_gemm(p0p_ctx* ctx, const p0p_gemm_args* a, double* flops);
 /* the kernel family the last successful p0p_gemm used (P0P_K_*), and how many kernels it launched */
 int p0p_last_kernel(const p0p_ctx* ctx);
 uint64_t p0p_launch_count(const p0p_ctx* ctx);
+/* Test convenience (no counterpart in the reference): the plan of the last call the tensor-core kernel served, so that tests can
+ * tell which variant they covered.  out8 = {tokens per tile, k-steps of 64 k per pipeline step, lock-step rings (0 / 1), token
+ * stages, operand stages, accumulator buffers, split-K units per tile, tiles left unsplit}. */
+int p0p_last_plan(const p0p_ctx* ctx, uint32_t* out8);
 
 /* No counterpart in the reference (a browser page never manages device memory).  The decode-sized q4 multiply
  * (M <= 16 tokens: y[M][N] fp16 = x[M][K] fp16 * W^T, W in q4g32a.t64) for callers that cannot allocate on the

@@ -16,7 +16,7 @@ SYMBOLS = [
     "p0p_write", "p0p_read", "p0p_clear", "p0p_copy", "p0p_sync", "p0p_host_alloc", "p0p_host_free",
     "p0p_capture_begin", "p0p_capture_end", "p0p_graph_launch", "p0p_graph_free",
     "p0p_decode_q4_static", "p0p_decode_q4_static_status", "p0p_alloc_shareable", "p0p_ipc_export", "p0p_ipc_open", "p0p_peer_barrier",
-    "p0p_gemm", "p0p_attention", "p0p_last_kernel", "p0p_launch_count", "p0p_dequant", "p0p_rowstats",
+    "p0p_gemm", "p0p_attention", "p0p_last_kernel", "p0p_launch_count", "p0p_last_plan", "p0p_dequant", "p0p_rowstats",
     "p0p_pixstats", "p0p_gn_partial", "p0p_gn_finalize",
     "p0p_f2h", "p0p_h2f", "p0p_to_f16", "p0p_from_f16", "p0p_pack_q4", "p0p_pack_q8", "p0p_reorder_conv_rows",
     "p0p_encoded_bytes", "p0p_shard_rows", "p0p_abi_version",
@@ -71,7 +71,7 @@ def _load():
         "p0p_gn_partial": (i, [vp, vp, u64, u32, u32, vp, u32, C.POINTER(u32)]),
         "p0p_gn_finalize": (i, [vp, vp, u32, u32, C.c_float, vp, u32, u32, vp, u32]),
         "p0p_alloc_shareable": (i, [vp, u64, C.POINTER(vp)]), "p0p_ipc_export": (i, [vp, vp, vp]), "p0p_ipc_open": (i, [vp, vp, u64, C.POINTER(vp)]),
-        "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_attention": (i, [vp, C.POINTER(AttnArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]),
+        "p0p_gemm": (i, [vp, C.POINTER(GemmArgs), C.POINTER(C.c_double)]), "p0p_attention": (i, [vp, C.POINTER(AttnArgs), C.POINTER(C.c_double)]), "p0p_last_kernel": (i, [vp]), "p0p_launch_count": (u64, [vp]), "p0p_last_plan": (i, [vp, C.POINTER(C.c_uint32)]),
         "p0p_dequant": (i, [vp, u32, vp, u64, u32, u32, u32, u32, u32, vp, u64]),
         "p0p_rowstats": (i, [vp, vp, u64, u32, u32, u32, u32, u32, C.c_float, vp, u32]),
         "p0p_f2h": (C.c_uint16, [C.c_float]), "p0p_h2f": (C.c_float, [C.c_uint16]),

@@ -34,6 +34,7 @@ struct p0p_ctx {
   uint64_t alive = 0, peak = 0, pooled = 0, pooledN = 0, hw = 0, maxBuf = 0, creates = 0, reuses = 0, evictions = 0, poolSeq = 0;
   // op bookkeeping
   int last_kernel = 0;
+  uint32_t last_plan[8] = {};   // the tensor-core kernel's plan of the last call (p0p_last_plan)
   uint64_t launches = 0;
   // split-K partial sums of the decode kernel (grown on demand, owned by the context)
   void* scratch = nullptr;

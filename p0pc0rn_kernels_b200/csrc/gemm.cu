@@ -22,6 +22,11 @@ inline bool live(const p0p_ctx* c, const p0p_buf* b) { return b && c->bufs.count
 
 extern "C" int p0p_last_kernel(const p0p_ctx* c) { return c ? c->last_kernel : 0; }
 extern "C" uint64_t p0p_launch_count(const p0p_ctx* c) { return c ? c->launches : 0; }
+extern "C" int p0p_last_plan(const p0p_ctx* c, uint32_t* out8) {
+  if (!c || !out8) return -1;
+  for (int i = 0; i < 8; i++) out8[i] = c->last_plan[i];
+  return 0;
+}
 
 extern "C" int p0p_gemm(p0p_ctx* c, const p0p_gemm_args* a_in, double* flops) {
   P0P_ALIVE(c);

@@ -280,6 +280,8 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   cudaError_t e = cudaSuccess;
   if (once[p.enc][variant][p.epi].run(c->device, [&] { e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max); return (int)e; }))
     return cuda_fail(c, e != cudaSuccess ? e : cudaErrorInvalidDevice, "tensor-core kernel attribute");
+  const uint32_t plan[8] = {u.BT, u.KW, u.LOCK, u.NS, u.NA, u.NACC, u.S, u.T0};
+  std::copy(plan, plan + 8, c->last_plan);
   void* args[3] = {&u, &mx, &mw};
   if ((e = cudaLaunchKernel(reinterpret_cast<const void*>(kern), dim3(grid), dim3(U_THREADS), args, smem, c->stream)) != cudaSuccess) return cuda_fail(c, e, "tensor-core kernel launch");
   c->launches += 1;

@@ -251,6 +251,13 @@ class Gpu:
         return lib.p0p_last_kernel(self._h)
 
     @property
+    def lastPlan(self) -> dict:
+        """the tensor-core kernel's plan of the last call it served (a test convenience)"""
+        out = (C.c_uint32 * 8)()
+        self._check(lib.p0p_last_plan(self._h, out))
+        return dict(zip(("BT", "KW", "LOCK", "NS", "NA", "NACC", "S", "T0"), (int(v) for v in out)))
+
+    @property
     def launches(self) -> int:
         return int(lib.p0p_launch_count(self._h))
 

@@ -365,6 +365,11 @@ UMMA = [
     dict(name="u split-K of the last round only (149 tiles)", enc="q4", M=64, N=128 * 149, K=1024),
     dict(name="u split-K of the last round only, rms+swiglu (150 tiles)", enc="q8", M=100, N=2 * 64 * 150, K=512, xmode="rms", epi="swiglu"),
     dict(name="u split-K of the last round only, wide tiles resadd (2 x 75 tiles)", enc="q4", M=600, N=128 * 75, K=768, epi="resadd"),
+    # 4-bit weights, tiles up to 128 tokens, 32 k-steps or more per unit (one tile per SM: no split): pipeline steps of 256 k, the
+    # last step of the k loop short by one, two and three k-steps; above 64 tokens with a single accumulator buffer
+    dict(name="u q4 M16 256-k steps, tail of one k-step", enc="q4", M=16, N=128 * 148, K=64 * 33),
+    dict(name="u q4 M100 256-k steps, tail of two k-steps, rms+swiglu", enc="q4", M=100, N=2 * 64 * 148, K=64 * 34, xmode="rms", epi="swiglu"),
+    dict(name="u q4 M64 256-k steps, tail of three k-steps, resadd", enc="q4", M=64, N=128 * 148, K=64 * 35, epi="resadd"),
     dict(name="u q4 M384 one wide tile, ring wrap", enc="q4", M=384, N=640, K=1280),
     dict(name="u q8 M777 wide tiles, many", enc="q8", M=777, N=2560, K=448, epi="resadd"),
     dict(name="u q4 M250 single accumulator, narrow", enc="q4", M=250, N=1280, K=192, epi="swiglu"),
@@ -395,6 +400,8 @@ def test_tensor_core_kernel(gpu, oracle, case):
     CS.check(got, CS.run_oracle(h), case["name"])
     got2 = CS.run_gpu(gpu, CS.build(dict(case)))
     assert gpu.lastKernel == K_UMMA and np.array_equal(got, got2)
+    if "256-k steps" in case["name"]:
+        assert gpu.lastPlan["KW"] == 4 and gpu.lastPlan["S"] == 1, gpu.lastPlan
 
 
 def test_tensor_core_matches_general_kernel_bits_of_weights(gpu, oracle):
