@@ -35,7 +35,10 @@ struct AttnTcP {
   int* status;           // bounded waits report here
 };
 
-constexpr uint32_t ATC_THREADS = 320u, ATC_TILE = 32768u, ATC_SLOTS = 4u;
+#ifndef ATC_SLOTS_N
+#define ATC_SLOTS_N 4
+#endif
+constexpr uint32_t ATC_THREADS = 320u, ATC_TILE = 32768u, ATC_SLOTS = ATC_SLOTS_N;
 constexpr uint32_t ATC_SMEM = 1024u + (2u + ATC_SLOTS) * ATC_TILE + 256u;      // alignment slack + Q tiles + ring + barriers
 
 #ifndef ATC_EMU
