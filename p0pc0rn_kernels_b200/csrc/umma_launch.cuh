@@ -196,7 +196,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // ... except where every tile above 128 tokens is split along K (few output columns): the units are short, and with 64-k steps
   // four stages fit where two of 128 k do, so a unit's fill and drain are half as long (measured: the LLM block's down GEMM at
   // 512 tokens 68.7 -> 64.2 us; unsplit tiles of that width lose 4 % that way)
-  if (atm && BT > 128u && BT <= 256u && u.S > 1u && u.T0 == 0u) u.KW = 1u;
+  if (atm && BT > 128u && BT <= 256u && u.S > 1u && u.T0 == 0u && u.ks_per >= 48u) u.KW = 1u;      // (long units only: 4096 x 4096 at 600 tokens lost 5 %)
   // 256 k for 4-bit weights on tiles up to 128 tokens: there each role's loop, not its work, is what a step costs (a record stage
   // of 4-bit weights is 256 k long; 8-bit stages are 128 k, so those keep 128-k steps).  Three operand stages of 128 columns
   // must fit behind the accumulators: one accumulator buffer above 64 tokens.  Not for units of few k-steps (split-K of a small
