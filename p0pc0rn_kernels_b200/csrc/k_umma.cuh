@@ -78,9 +78,10 @@ struct UmmaP {
 // two bulk copies of KSUP * RB bytes (the records of one row tile are consecutive along K), 64 bytes apart in
 // shared memory so that the two tiles fall into different banks.  Large copies matter: the copy engine's request
 // rate, not its byte rate, bounds many small copies.
-template <int ENC> struct UQ { static constexpr uint32_t REC = 0, REC_K = 64, RB = 0, KSUP = 1, STAGE = 0; };
-template <> struct UQ<P0P_ENC_Q4> { static constexpr uint32_t REC = 1280, REC_K = 32, RB = 2560, KSUP = 4, STAGE = 2 * 4 * 2560 + 128; };
-template <> struct UQ<P0P_ENC_Q8> { static constexpr uint32_t REC = 4224, REC_K = 64, RB = 4224, KSUP = 2, STAGE = 2 * 2 * 4224 + 128; };
+// (KW: the pipeline step of the kernel variant; a record stage holds at least one whole step.)
+template <int ENC, int KW = 1> struct UQ { static constexpr uint32_t REC = 0, REC_K = 64, RB = 0, KSUP = 1, STAGE = 0; };
+template <int KW> struct UQ<P0P_ENC_Q4, KW> { static constexpr uint32_t REC = 1280, REC_K = 32, RB = 2560, KSUP = 4, STAGE = 2 * KSUP * RB + 128; };
+template <int KW> struct UQ<P0P_ENC_Q8, KW> { static constexpr uint32_t REC = 4224, REC_K = 64, RB = 4224, KSUP = KW > 2 ? KW : 2, STAGE = 2 * KSUP * RB + 128; };
 
 __device__ __forceinline__ uint4 u_lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint32_t u_lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   extern __shared__ unsigned char smem_raw[];
   constexpr bool ATM = ENC != P0P_ENC_F16;
   constexpr uint32_t KW = KW_;
+  using Q = UQ<ENC, KW_>;
   constexpr bool lock = LOCK_;
   const KP& p = u.p;
   const uint32_t BT = u.BT, NS = u.NS, NQ = u.NQ;
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
   const uint32_t XT = BT * 128u, XS = KW * XT;                                     // bytes of a token sub-tile (64 k) and of a stage
   const uint32_t a_st = base, x_st = a_st + (ATM ? 0u : NS * U_A_BYTES), q_st = x_st + NS * XS;
   const uint32_t acc_stride = u.acc_stride;
-  const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * UQ<ENC>::STAGE);
+  const uint32_t epi_sh = q_st + (ENC == P0P_ENC_F16 ? 0u : NQ * Q::STAGE);
   const uint32_t bars = epi_sh + (uint32_t)U_EPI_BYTES;
   float* epi_ptr = reinterpret_cast<float*>(gbase + (epi_sh - base));
   // barrier slots (8 bytes each)
@@ -242,14 +244,14 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
         uint32_t trow[2];
         if (swiglu) { trow[0] = min((p.wR0 + nt * 64u) >> 6, last); trow[1] = min((p.wR1 + nt * 64u) >> 6, last); }
         else { trow[0] = min((p.wR0 + nt * 128u) >> 6, last); trow[1] = min(trow[0] + 1u, last); }
-        const unsigned char* src0 = p.W + ((size_t)trow[0] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
-        const unsigned char* src1 = p.W + ((size_t)trow[1] * p.wG + p.wk0 / UQ<ENC>::REC_K) * UQ<ENC>::REC;
-        for (uint32_t ks = kb; ks < ke; ks += UQ<ENC>::KSUP, q.next()) {
-          const uint32_t bytes = min(UQ<ENC>::KSUP, ke - ks) * UQ<ENC>::RB;
+        const unsigned char* src0 = p.W + ((size_t)trow[0] * p.wG + p.wk0 / Q::REC_K) * Q::REC;
+        const unsigned char* src1 = p.W + ((size_t)trow[1] * p.wG + p.wk0 / Q::REC_K) * Q::REC;
+        for (uint32_t ks = kb; ks < ke; ks += Q::KSUP, q.next()) {
+          const uint32_t bytes = min(Q::KSUP, ke - ks) * Q::RB;
           if (!mbar_wait(wq_empty + 8u * q.s, q.ph ^ 1u, u.status, 202, 200u)) { ok = false; break; }
           mbar_expect_tx(wq_full + 8u * q.s, 2u * bytes);
-          bulk_g2s(q_st + q.s * UQ<ENC>::STAGE, src0 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
-          bulk_g2s(q_st + q.s * UQ<ENC>::STAGE + UQ<ENC>::KSUP * UQ<ENC>::RB + 64u, src1 + (size_t)ks * UQ<ENC>::RB, bytes, wq_full + 8u * q.s);
+          bulk_g2s(q_st + q.s * Q::STAGE, src0 + (size_t)ks * Q::RB, bytes, wq_full + 8u * q.s);
+          bulk_g2s(q_st + q.s * Q::STAGE + Q::KSUP * Q::RB + 64u, src1 + (size_t)ks * Q::RB, bytes, wq_full + 8u * q.s);
         }
       }
     }
@@ -356,7 +358,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     // sub-step `grp` of every step (KW = 2; a step whose second sub-step does not exist still gets group 1's arrival).
     const uint32_t r = (warp & 3u) * 32u + lane, grp = (warp - 6u) >> 2;
     const uint32_t tsel = swiglu ? (r & 1u) : (r >> 6), rr = swiglu ? (r >> 1) : (r & 63u);
-    const uint32_t tile_off = tsel * (UQ<ENC>::KSUP * UQ<ENC>::RB + 64u);
+    const uint32_t tile_off = tsel * (Q::KSUP * Q::RB + 64u);
     const uint32_t rec_row = tile_off + (ENC == P0P_ENC_Q4 ? rr * 16u : rr * 64u);
     const uint32_t rec_sm = tile_off + (ENC == P0P_ENC_Q4 ? 1024u + rr * 4u : 4096u + rr * 2u);
     const uint32_t ta0 = tmem_base + (((warp & 3u) * 32u) << 16) + u.a_col0;
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     bool ok = true;
     // one operand row of k-step jj of the record stage -> 32 columns of tensor memory at ta
     auto convert = [&](uint32_t jj, uint32_t ta) {
-      const uint32_t rec = q_st + qr.s * UQ<ENC>::STAGE + jj * UQ<ENC>::RB;
+      const uint32_t rec = q_st + qr.s * Q::STAGE + jj * Q::RB;
       if (ENC == P0P_ENC_Q4) {
         // both 32-k halves of the row are fetched first, so that the second half's loads are in flight while the first converts
         const uint4 c0 = u_lds128(rec + rec_row), c1 = u_lds128(rec + rec_row + 1280u);
@@ -397,8 +399,8 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
     };
     for (uint32_t unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
       const UnitOf un = unit_of(u, unit, tiles, KS); const uint32_t n = un.ke - un.kb;
-      for (uint32_t j0 = 0; j0 < n && ok; j0 += UQ<ENC>::KSUP, qr.next()) {
-        const uint32_t cnt = min(UQ<ENC>::KSUP, n - j0);
+      for (uint32_t j0 = 0; j0 < n && ok; j0 += Q::KSUP, qr.next()) {
+        const uint32_t cnt = min(Q::KSUP, n - j0);
         bool fresh = true;                                         // the record stage is awaited at this group's first k-step in it
         if (ALT) {
           // the stage's steps (KW k-steps each, the last may be short); this group's are those of its parity in the running count

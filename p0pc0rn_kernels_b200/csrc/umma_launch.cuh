@@ -197,11 +197,12 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // four stages fit where two of 128 k do, so a unit's fill and drain are half as long (measured: the LLM block's down GEMM at
   // 512 tokens 68.7 -> 64.2 us; unsplit tiles of that width lose 4 % that way)
   if (atm && BT > 128u && BT <= 256u && u.S > 1u && u.T0 == 0u && u.ks_per >= 48u) u.KW = 1u;      // (long units only: 4096 x 4096 at 600 tokens lost 5 %)
-  // 256 k for 4-bit weights on tiles up to 128 tokens: there each role's loop, not its work, is what a step costs (a record stage
-  // of 4-bit weights is 256 k long; 8-bit stages are 128 k, so those keep 128-k steps).  Three operand stages of 128 columns
+  // 256 k for quantised weights on tiles up to 128 tokens: there each role's loop, not its work, is what a step costs (a record
+  // stage is then one such step: 8 KB per 64-row tile of 4-bit weights, 17 KB of 8-bit ones).  Three operand stages of 128 columns
   // must fit behind the accumulators: one accumulator buffer above 64 tokens.  Not for units of few k-steps (split-K of a small
   // weight): two or three such steps would be all fill and drain.
-  if (p.enc == P0P_ENC_Q4 && BT <= 128u && u.ks_per >= 32u) { u.KW = 4u; if (BT > 64u) u.NACC = 1u; }
+  // (8-bit weights up to 96 tokens: beyond, their 34-KB record stages and the 64-KB token stages leave two of each)
+  if (atm && BT <= (p.enc == P0P_ENC_Q4 ? 128u : 96u) && u.ks_per >= 32u) { u.KW = 4u; if (BT > 64u) u.NACC = 1u; }
 #ifdef P0P_KNOBS
   if (const char* e = getenv("P0P_NACC")) u.NACC = (uint32_t)atoi(e);
   if (const char* e = getenv("P0P_KW")) u.KW = (uint32_t)atoi(e);
@@ -213,8 +214,11 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if (!atm) { u.NS = BT > 192u ? 3u : 4u; u.NA = u.NS; u.LOCK = 1u; }
   else {
     u.NA = std::min<uint32_t>(U_NA_MAX, (512u - u.a_col0) / (32u * u.KW));
+    // (shared memory: up to 144 KB of token stages, less where three record stages would not fit beside them)
     const uint32_t xstage = u.KW * BT * 128u;
-    u.NS = std::max(2u, std::min<uint32_t>(U_NX_MAX, (144u * 1024u) / xstage));
+    const uint32_t qst = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : (u.KW == 4u ? UQ<P0P_ENC_Q8, 4>::STAGE : UQ<P0P_ENC_Q8>::STAGE);
+    const uint32_t xroom = std::min<uint32_t>(144u * 1024u, 227u * 1024u - 20u * 1024u - 3u * qst);
+    u.NS = std::max(2u, std::min<uint32_t>(U_NX_MAX, xroom / xstage));
     u.LOCK = 0u;
     // Tiles above 128 tokens are bound by the multiplies, and there every instruction the issuing warp runs between two
     // multiplies shows: the two rings advance in lock step on shared barriers (one wait, one commit per step).
@@ -227,7 +231,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if (u.LOCK) u.NA = u.NS = std::min(u.NS, u.NA);
 #endif
   // record stages: as many as fit beside the operand stages, up to about 100 KB in flight
-  const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? UQ<P0P_ENC_Q8>::STAGE : 0;
+  const size_t qstage = p.enc == P0P_ENC_Q4 ? UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? (u.KW == 4u ? UQ<P0P_ENC_Q8, 4>::STAGE : UQ<P0P_ENC_Q8>::STAGE) : 0;
   const size_t fixed = 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * u.KW * BT * 128u + (size_t)U_EPI_BYTES + 1024u;
   size_t q_cap = 100 * 1024;
 #ifdef P0P_KNOBS
@@ -271,7 +275,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   if (p.enc == P0P_ENC_F16) {
     if (!make_map(&mw, reinterpret_cast<const __half*>(p.W) + p.wk0, p.K, p.Nw, p.wG, 128u)) return fail(c, -12, "gemm: the weight tensor map could not be encoded");
   } else mw = mx;
-  const size_t qbytes = p.enc == P0P_ENC_Q4 ? u.NQ * UQ<P0P_ENC_Q4>::STAGE : p.enc == P0P_ENC_Q8 ? u.NQ * UQ<P0P_ENC_Q8>::STAGE : 0;
+  const size_t qbytes = u.NQ * qstage;
   // at least 120 KB: one block per SM, so that a block never waits for another's tensor memory
   const size_t smem = std::max<size_t>(120 * 1024, 1024 + (atm ? 0 : (size_t)u.NS * U_A_BYTES) + (size_t)u.NS * u.KW * BT * 128u + qbytes + (size_t)U_EPI_BYTES + 1024u);
   const int grid = (int)std::min<uint64_t>((uint64_t)u.T0 + (uint64_t)(tiles_all - u.T0) * u.S, sms);

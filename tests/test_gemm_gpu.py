@@ -365,11 +365,13 @@ UMMA = [
     dict(name="u split-K of the last round only (149 tiles)", enc="q4", M=64, N=128 * 149, K=1024),
     dict(name="u split-K of the last round only, rms+swiglu (150 tiles)", enc="q8", M=100, N=2 * 64 * 150, K=512, xmode="rms", epi="swiglu"),
     dict(name="u split-K of the last round only, wide tiles resadd (2 x 75 tiles)", enc="q4", M=600, N=128 * 75, K=768, epi="resadd"),
-    # 4-bit weights, tiles up to 128 tokens, 32 k-steps or more per unit (one tile per SM: no split): pipeline steps of 256 k, the
+    # quantised weights, tiles up to 128 tokens, 32 k-steps or more per unit (one tile per SM: no split): pipeline steps of 256 k, the
     # last step of the k loop short by one, two and three k-steps; above 64 tokens with a single accumulator buffer
     dict(name="u q4 M16 256-k steps, tail of one k-step", enc="q4", M=16, N=128 * 148, K=64 * 33),
     dict(name="u q4 M100 256-k steps, tail of two k-steps, rms+swiglu", enc="q4", M=100, N=2 * 64 * 148, K=64 * 34, xmode="rms", epi="swiglu"),
     dict(name="u q4 M64 256-k steps, tail of three k-steps, resadd", enc="q4", M=64, N=128 * 148, K=64 * 35, epi="resadd"),
+    dict(name="u q8 M48 256-k steps, tail of two k-steps", enc="q8", M=48, N=128 * 148, K=64 * 34),
+    dict(name="u q8 M90 256-k steps, tail of three k-steps, rms+swiglu", enc="q8", M=90, N=2 * 64 * 148, K=64 * 35, xmode="rms", epi="swiglu"),
     dict(name="u q4 M384 one wide tile, ring wrap", enc="q4", M=384, N=640, K=1280),
     dict(name="u q8 M777 wide tiles, many", enc="q8", M=777, N=2560, K=448, epi="resadd"),
     dict(name="u q4 M250 single accumulator, narrow", enc="q4", M=250, N=1280, K=192, epi="swiglu"),
