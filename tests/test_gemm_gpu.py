@@ -447,6 +447,12 @@ DECODE = [
     dict(name="d sub-ranges M4", enc="q4", M=4, N=128, K=256, ldx=448, kx0=64, wk0=160, w_cols=512, wr0=64, w_rows=256, ldy=200, ny0=40),
     dict(name="d sub-ranges q8 M4", enc="q8", M=4, N=128, K=256, ldx=456, kx0=66, wk0=128, w_cols=512, wr0=64, w_rows=256, ldy=200, ny0=40),
     dict(name="d byte offsets M2", enc="q8", M=2, N=128, K=256, x_off=256, w_off=512, y_off=768),
+    # more units than resident blocks: the stages are dealt out evenly and units are shared by two blocks (part 0 / part 1 of the
+    # partial sums), with a short last k-block; and so many units that the ranges are rounded to whole units again
+    dict(name="d q4 M3 shared units, short last k-block", enc="q4", M=3, N=64 * 300, K=4096 + 1024),
+    dict(name="d q8 M1 shared units, short last k-block", enc="q8", M=1, N=64 * 500, K=2048 + 256),
+    dict(name="d q4 M2 shared units, rms+swiglu", enc="q4", M=2, N=2 * 64 * 250, K=4096, xmode="rms", epi="swiglu"),
+    dict(name="d q4 M2 whole-unit ranges (1800 units)", enc="q4", M=2, N=64 * 1800, K=512),
     dict(name="d K not a stage multiple -> general kernel", enc="q4", M=2, N=128, K=384, expect="generic"),
 ]
 
