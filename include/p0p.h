@@ -151,7 +151,9 @@ int p0p_last_kernel(const p0p_ctx* ctx);
 uint64_t p0p_launch_count(const p0p_ctx* ctx);
 /* Test convenience (no counterpart in the reference): the plan of the last call the tensor-core kernel served, so that tests can
  * tell which variant they covered.  out8 = {tokens per tile, k-steps of 64 k per pipeline step, lock-step rings (0 / 1), token
- * stages, operand stages, accumulator buffers, split-K units per tile, tiles left unsplit}. */
+ * stages, operand stages, accumulator buffers, split-K units per tile, tiles left unsplit}.  After a call the decode kernel
+ * served: {blocks, stages of 256 k in the call, k-block length, k-blocks, 1 if the blocks' ranges are whole units, units, 64-row
+ * tiles, 0}. */
 int p0p_last_plan(const p0p_ctx* ctx, uint32_t* out8);
 
 /* No counterpart in the reference (a browser page never manages device memory).  The decode-sized q4 multiply

@@ -98,6 +98,8 @@ int launch_decode(p0p_ctx* c, const KP& p) {
   if (int r = ensure_scratch(c, sbytes + 256)) return r;
   d.scratch = reinterpret_cast<float*>(c->scratch);
   d.status = c->dev_status;
+  const uint32_t plan[8] = {d.G, d.T, d.KC, d.S, d.whole, d.units, d.tiles, 0u};
+  std::copy(plan, plan + 8, c->last_plan);
   const cudaError_t e = launch_decode_pair(d, L, c->device, c->stream);
   if (e != cudaSuccess) return cuda_fail(c, e, "decode launch");
   c->launches += 2;

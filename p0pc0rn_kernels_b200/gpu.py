@@ -255,7 +255,10 @@ class Gpu:
         """the tensor-core kernel's plan of the last call it served (a test convenience)"""
         out = (C.c_uint32 * 8)()
         self._check(lib.p0p_last_plan(self._h, out))
-        return dict(zip(("BT", "KW", "LOCK", "NS", "NA", "NACC", "S", "T0"), (int(v) for v in out)))
+        v = [int(x) for x in out]
+        if self.lastKernel == 2:      # the decode kernel
+            return dict(zip(("G", "T", "KC", "S", "whole", "units", "tiles"), v))
+        return dict(zip(("BT", "KW", "LOCK", "NS", "NA", "NACC", "S", "T0"), v))
 
     @property
     def launches(self) -> int:

@@ -470,6 +470,10 @@ def test_decode_kernel(gpu, oracle, case):
     h = CS.build(dict(case, kernel="decode"))
     got = CS.run_gpu(gpu, h)
     assert gpu.lastKernel == K_DECODE
+    plan = gpu.lastPlan
+    if "shared units" in case["name"]:                           # the blocks' ranges are not whole units: some unit has two parts
+        assert not plan["whole"] and plan["G"] < plan["units"] and (plan["T"] % plan["G"] or (plan["T"] // plan["G"]) % (plan["KC"] // 256)), plan
+    if "whole-unit ranges" in case["name"]: assert plan["whole"] and plan["units"] >= 4 * plan["G"], plan
     CS.check(got, CS.run_oracle(h), case["name"])
     h2 = CS.build(dict(case))                                   # the library's own pick: this kernel up to 8 tokens, the tensor-core kernel from 9
     got2 = CS.run_gpu(gpu, h2)
