@@ -339,6 +339,11 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
           for (int j = 0; j < U_EPI_TB; j++) acc[j] += ok ? __uint_as_float(r[j]) : 0.0f;
         }
         if (ch + 1u < nchunks) tmem_ld16(t0 + (ch + 1u) * U_EPI_TB, r);      // the next pass's accumulators load behind this pass's work
+        else {                                                   // the tile's last values are in registers: the accumulator is free for
+          tc_fence_before();                                     // the next tile's multiplies while this pass still computes and stores
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+        }
         if (un.split) {
           // split-K: this unit's partial sums, fp32, to its own slab; a warp's store covers 128 bytes of a row
           float* dst = u.sk_part + (((size_t)sp * (tiles - u.T0) + (tile - u.T0)) * BT + ch * U_EPI_TB) * 128u + c;
@@ -346,9 +351,11 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_gemm_umma(const UmmaP u, const
           for (int j = 0; j < U_EPI_TB; j++) dst[(size_t)j * 128u] = acc[j];
         } else epilogue_cols<U_EPI_TB, EPI>(p, m0 + ch * U_EPI_TB, nt * 128u, c, acc, epi_ptr, 2, vec, pass & 1u);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+      if (nchunks == 0u) {                                       // (cannot happen: a tile has tokens; kept so that the barrier's count never slips)
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+      }
     }
   } else if (ENC != P0P_ENC_F16 && warp < 6u + U_DEQ_WARPS) {
     // ================================================================= dequantisation: codes -> fp16 operand rows in tensor
