@@ -203,7 +203,7 @@ inline int launch_umma(p0p_ctx* c, const KP& p0) {
   // weight): two or three such steps would be all fill and drain.
   // (8-bit weights up to 96 tokens: beyond, their 34-KB record stages and the 64-KB token stages leave two of each)
   if (atm && BT <= (p.enc == P0P_ENC_Q4 ? 128u : 96u) && u.ks_per >= 32u) { u.KW = 4u; if (BT > 64u) u.NACC = 1u; }
-#ifdef P0P_KNOBS
+#ifdef P0P_KNOBS      // (tuning experiments only: a library built with -DP0P_KNOBS lets environment variables override the plan)
   if (const char* e = getenv("P0P_NACC")) u.NACC = (uint32_t)atoi(e);
   if (const char* e = getenv("P0P_KW")) u.KW = (uint32_t)atoi(e);
 #endif
