@@ -6,8 +6,8 @@
 One step = one pass of the block over M tokens (default 512): row statistics, the fused gate/up GEMM, the fused
 down GEMM.  `value` is TFLOP/s (2*M*N*K of both GEMMs over the device time of K steps, inputs resident in HBM);
 `e2e` is the same through the public API with HOST buffers (page-locked host -> device copy of the tokens and a
-device -> host read of the result inside the timed region; at N = 1 the steps run as a three-stream pipeline - upload,
-block, read-back over a ring of residual buffers - and the plain one-after-the-other loop is reported beside it).
+device -> host read of the result inside the timed region; the steps run as a three-stream pipeline - upload, block,
+read-back over a ring of residual buffers - and the plain one-after-the-other loop is reported beside it).
 Decode-sized M (1, 16) is measured next to it and reported as GB/s of the weight stream in `cases`.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m 512]
@@ -463,8 +463,10 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
         """every rank's columns are in every copy once all ranks are past this point of their streams"""
         if fused: gpu.peerBarrier(flags, flag_peers, rank, world, BARRIER_CYCLES)
 
-    def block(M, i, gather=True, xb=xb):
-        """one pass of the MLP block over M tokens with weight copy i (xb: the residual stream it updates in place)"""
+    def block(M, i, gather=True, xb=xb, xp=None):
+        """one pass of the MLP block over M tokens with weight copy i (xb: the residual stream it updates in place; xp: the other
+        ranks' copies of that buffer)"""
+        xp = x_peers if xp is None else xp
         P.rowstats(gpu, {"x": {"buf": xb}, "rows": M, "cols": HID, "mode": "rms", "eps": 1e-6, "st": {"buf": st}})
         yh = {"buf": hf, "ld": FF, "n0": rank * ffl, "peers": hf_peers} if fused else {"buf": hl, "ld": ffl}
         a = {"w": {"enc": "q4g32a.t64", "buf": Wgu[i], "off": 0, "bytes": gu_mine.nbytes, "rows": 2 * ffl, "cols": HID}, "x": {"buf": xb, "mode": "rms"},
@@ -476,7 +478,7 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
             hf_t[: M * FF].view(M, FF).copy_(P.all_gather_columns(hl_t[: M * ffl].view(M, ffl)))
         # residual add, in place, into this rank's columns of the (replicated) fp32 residual stream
         a = {"w": {"enc": "q4g32a.t64", "buf": Wdn[i], "off": 0, "bytes": dn_mine.nbytes, "rows": hidl, "cols": FF}, "x": {"buf": hf},
-             "y": {"buf": xb, "ld": HID, "n0": rank * hidl, "peers": x_peers if fused else []}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
+             "y": {"buf": xb, "ld": HID, "n0": rank * hidl, "peers": xp if fused else []}, "M": M, "N": hidl, "K": FF, "epi": "resadd"}
         if args.kernel: a["kernel"] = args.kernel
         P.gemm(gpu, a)
         if fused and gather: order_ranks()
@@ -590,16 +592,39 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
     h2d = M * HID * 4
     e2e = {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms,
            "pipeline": "none: upload, block, read-back one after the other on one stream"}
-    # ---- N = 1: the same steps as a serving loop would run them: three contexts of the library on three streams (upload / block /
+    # ---- the same steps as a serving loop would run them: three contexts of the library on three streams (upload / block /
     # read-back) over a ring of three residual buffers, so that step i's block runs while step i + 1's tokens arrive and step
     # i - 1's result leaves.  Every step still makes its own host -> device copy from page-locked memory and its own device ->
-    # host read through the public API, inside the timed region.  (N > 1 keeps the plain loop: the peers' copies of the residual
-    # are fixed buffers.)
-    if world == 1:
-        NB = 3
+    # host read through the public API, inside the timed region.  N > 1: every rank maps the others' three buffers (the down
+    # GEMM stores into the peers' copy of the step's buffer); the barriers inside each step keep the ranks in lockstep, so a
+    # buffer is only written by peers between its owner's upload and its owner's read-back.  (With the NCCL gather path the
+    # plain loop stays.)
+    NB = 3
+    pipe_ok = world == 1 or fused
+    xbs, xps = [], [[] for _ in range(NB)]
+    if pipe_ok:
+        mine, err = None, None
+        try:
+            xbs = [gpu.buffer(M * HID * 4, f"residual.{b}", shareable=world > 1) for b in range(NB)]
+            if world > 1: mine = [gpu.ipcExport(b) for b in xbs]
+        except Exception as e:
+            err = str(e); pipe_ok = False
+        if world > 1:
+            every = [None] * world
+            dist.all_gather_object(every, mine)
+            if pipe_ok and all(h is not None for h in every):
+                try:
+                    for r in range(world):
+                        if r != rank:
+                            for b in range(NB): xps[b].append(gpu.ipcOpen(every[r][b], M * HID * 4, f"residual.{b}@{r}"))
+                except Exception as e:
+                    err = str(e); pipe_ok = False
+            else: pipe_ok = False
+            ok_t = torch.tensor([1 if pipe_ok else 0], device=dev); dist.all_reduce(ok_t, op=dist.ReduceOp.MIN); pipe_ok = bool(ok_t.item())
+            if not pipe_ok and rank == 0: print(f"pipelined end-to-end leg skipped ({err})", file=sys.stderr)
+    if pipe_ok:
         s_up, s_dn = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         g_up = P.createGpu({"device": local, "stream": s_up.cuda_stream}); g_dn = P.createGpu({"device": local, "stream": s_dn.cuda_stream})
-        xbs = [gpu.buffer(M * HID * 4, f"residual.{b}") for b in range(NB)]
         up_view = [g_up.wrap(b.ptr, M * HID * 4) for b in xbs]; dn_view = [g_dn.wrap(b.ptr, M * HID * 4) for b in xbs]
         hu = C.c_void_p(); g_up._check(lib.p0p_host_alloc(g_up._h, M * HID * 4, C.byref(hu)))
         pin_up = np.ctypeslib.as_array(C.cast(hu, C.POINTER(C.c_float)), shape=(M * HID,)); pin_up[:] = x_host[: M * HID]
@@ -610,9 +635,9 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
         graphs = {}
         for b in range(NB):
             for i in range(args.copies):
-                block(M, i, True, xbs[b]); torch.cuda.synchronize()
+                block(M, i, True, xbs[b], xps[b]); torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream): block(M, i, True, xbs[b])
+                with torch.cuda.graph(g, stream=stream): block(M, i, True, xbs[b], xps[b])
                 graphs[(b, i)] = g
         ev_up = [torch.cuda.Event() for _ in range(NB)]; ev_c = [torch.cuda.Event() for _ in range(NB)]; ev_dn = [torch.cuda.Event() for _ in range(NB)]
 
@@ -635,16 +660,23 @@ def run_block(args, P, torch, dist, gpu, stream, dev, pk, rank, world, local):
 
         pipelined(6); torch.cuda.synchronize()
         n_p = max(10, min(args.steps, 60))
+        if world > 1: dist.barrier()
         t0 = time.perf_counter(); pipelined(n_p); torch.cuda.synchronize()
         p_ms = (time.perf_counter() - t0) / n_p * 1e3
         # the pipelined result is the plain loop's: same tokens in, same bits out
         same = bool(np.array_equal(pin_dn[(n_p - 1) % NB], pin_out))
+        if world > 1:
+            t = torch.tensor([p_ms, 0.0 if same else 1.0], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); p_ms = float(t[0].item()); same = float(t[1].item()) == 0.0
         e2e = {"value": block_flops(M) / (p_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes, "ms_per_step": p_ms,
                "pipeline": "3 streams (upload / block / read-back) over a ring of 3 residual buffers; every step copies its tokens in and its result out",
                "unpipelined": {"value": block_flops(M) / (e2e_ms * 1e-3) / 1e12, "ms_per_step": e2e_ms}, "matches_unpipelined_bits": same}
         for v in up_view: g_up.free(v)
         for v in dn_view: g_dn.free(v)
         del graphs
+        torch.cuda.synchronize()
+        if world > 1: dist.barrier()               # nobody unmaps a buffer a peer's last step may still store into
+        for b in range(NB):
+            for q in xps[b]: gpu.free(q)
         for b in xbs: gpu.free(b)
 
     # ---- N > 1: one more block from the same tokens, checked.  Every rank's copy of the hidden row and of the residual must
